@@ -1,0 +1,155 @@
+/*
+ * b200q - affine group-wise quantized matmul for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libb200q.so.  Every entry point replaces one backend function of the
+ * reference project (paths are relative to the reference project root):
+ *
+ *   b200q_quantize        fast::Quantize::eval_gpu (dequantize_ == false)
+ *                         mlx/backend/cuda/quantized/quantized.cpp:280-324, numerics of
+ *                         quantize<T,U> mlx/backend/cpu/quantized.cpp:1148-1211
+ *   b200q_dequantize      fast::Quantize::eval_gpu (dequantize_ == true), same file;
+ *                         numerics of the op-composed form mlx/ops.cpp:5285-5327
+ *   b200q_qmm             QuantizedMatmul::eval_gpu
+ *                         mlx/backend/cuda/quantized/quantized.cpp:15-152
+ *   b200q_gather_qmm      GatherQMM::eval_gpu
+ *                         mlx/backend/cuda/quantized/quantized.cpp:154-278
+ *   b200q_qmm_host        the same operator called with host buffers (copies inside)
+ *
+ * Conventions
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void*
+ *     (NULL = the legacy default stream);
+ *   - all device pointers must be valid on the CURRENT device of the calling thread;
+ *   - calls only enqueue work on `stream`; they never synchronise, never allocate and
+ *     never free device memory.  Scratch memory is passed in by the caller and sized
+ *     with the matching *_workspace_bytes() query.  The first bytes of a workspace
+ *     hold self-cleaning counters: zero the workspace once after allocating it
+ *     (b200q_workspace_init) and never share one workspace between two calls that
+ *     may overlap on the GPU;
+ *   - return value: 0 on success; negative = rejected on the host before any launch
+ *     (see the B200Q_ERR_* codes; the text of the last error of the calling thread is
+ *     returned by b200q_last_error()).  B200Q_ERR_INVALID_ARGUMENT corresponds to the
+ *     reference's std::invalid_argument (Python ValueError), B200Q_ERR_UNSUPPORTED to
+ *     its std::runtime_error "no implementation for problem shape";
+ *   - packed weights use the reference layout: each row is a little-endian LSB-first
+ *     bit stream, value k in bits [k*bits, (k+1)*bits), viewed as uint32 words
+ *     (mlx/backend/cpu/quantized.cpp:1184-1206); scales and biases have one entry
+ *     per group of `group_size` consecutive values of a row.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200Q_VERSION 1
+
+/* element types of x / scales / biases / y */
+#define B200Q_F32 0
+#define B200Q_F16 1
+#define B200Q_BF16 2
+
+#define B200Q_OK 0
+#define B200Q_ERR_INVALID_ARGUMENT (-1)
+#define B200Q_ERR_UNSUPPORTED (-2)
+#define B200Q_ERR_CUDA (-3)
+#define B200Q_ERR_WORKSPACE (-4)
+#define B200Q_ERR_DEVICE (-5) /* device-side status word reported a bounded wait expired */
+
+int b200q_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* b200q_last_error(void);
+
+/*
+ * Per-group min/max, scale, bias and pack (bit-exact with the reference CPU quantize).
+ *   w       [rows, K]  dtype, row-contiguous          (in)
+ *   wq      [rows, K*bits/32] uint32                   (out)
+ *   scales  [rows, K/group_size] dtype                 (out)
+ *   biases  [rows, K/group_size] dtype                 (out)
+ * Requires group_size in {32,64,128}, bits in {2,3,4,5,6,8}, K % group_size == 0.
+ */
+int b200q_quantize(const void* w, int dtype, int64_t rows, int64_t K, int group_size, int bits,
+                   uint32_t* wq, void* scales, void* biases, void* stream);
+
+/*
+ * out[r,k] = round_T(round_T(q[r,k] * scales[r,k/g]) + biases[r,k/g]).
+ *   out [rows, K] dtype.
+ */
+int b200q_dequantize(const uint32_t* wq, const void* scales, const void* biases, int dtype,
+                     int64_t rows, int64_t K, int group_size, int bits, void* out, void* stream);
+
+/*
+ * y[b] = x[b] * dequant(w[b])^T   (transpose != 0;  wq [N, K*bits/32], scales [N, K/g])
+ * y[b] = x[b] * dequant(w[b])     (transpose == 0;  wq [K, N*bits/32], scales [K, N/g])
+ *   x [batch, M, K], y [batch, M, N]  dtype, row-contiguous
+ *   w_batch_stride: 0 = one weight matrix shared by all batches (x is then treated as
+ *   [batch*M, K]); otherwise 1 = wq/scales/biases hold `batch` consecutive matrices.
+ *   ws/ws_bytes: scratch of at least b200q_qmm_workspace_bytes(...) bytes (may be NULL
+ *   when that query returns 0).
+ * Accumulation is in float32; results are rounded once to dtype.
+ */
+size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                 int group_size, int bits, int transpose);
+int b200q_qmm(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* y,
+              int dtype, int64_t batch, int64_t M, int64_t N, int64_t K, int group_size, int bits,
+              int transpose, int64_t w_batch_stride, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * out[i] = x[lhs_idx[i]] (M x K) * dequant(w[rhs_idx[i]])   for i in [0, n_idx)
+ *   x [x_batch, M, K]; wq [E, ...], scales/biases [E, ...]; lhs_idx/rhs_idx uint32 [n_idx]
+ *   (already broadcast against each other, as the reference front-end does,
+ *   mlx/ops.cpp:5591-5594); y [n_idx, M, N].
+ *   sorted_flags: bit0 = lhs indices sorted, bit1 = rhs indices sorted (hints only).
+ * Index values are range-checked on the device; an out-of-range index leaves the
+ * corresponding output rows zero and sets the status word (see b200q_read_status).
+ */
+size_t b200q_gather_qmm_workspace_bytes(int dtype, int64_t n_idx, int64_t x_batch, int64_t E,
+                                        int64_t M, int64_t N, int64_t K, int group_size, int bits,
+                                        int transpose);
+int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                     const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* y,
+                     int dtype, int64_t x_batch, int64_t E, int64_t M, int64_t N, int64_t K,
+                     int group_size, int bits, int transpose, int sorted_flags, void* ws,
+                     size_t ws_bytes, void* stream);
+
+/* Zero a freshly allocated workspace (enqueued on `stream`). */
+int b200q_workspace_init(void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Device status word: kernels never trap; a bounded wait that expires or a bad gather
+ * index records a non-zero code in the last 16 bytes of the workspace.  This helper
+ * synchronises `stream`, copies the word to the host, clears it and returns it in
+ * *status (0 = clean).
+ */
+int b200q_read_status(void* ws, size_t ws_bytes, void* stream, uint32_t status[4]);
+
+/*
+ * Host-buffer form of b200q_qmm for callers that hold activations in host memory:
+ * copies x (host, ideally pinned) to x_dev, runs the operator, copies y_dev back to
+ * y_host, all on `stream`, and returns without synchronising.  Weights, scales and
+ * biases are device resident.  x_dev / y_dev are caller-provided device staging
+ * buffers of M*K and M*N elements.
+ */
+int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* wq, const void* scales,
+                   const void* biases, void* y_dev, void* y_host, int dtype, int64_t M, int64_t N,
+                   int64_t K, int group_size, int bits, int transpose, void* ws, size_t ws_bytes,
+                   void* stream);
+
+/*
+ * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
+ * launch for this problem ("qmv_bulk", "qmv_mma", "qmm_tcgen05", "qmm_generic").
+ */
+const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                  int group_size, int bits, int transpose);
+
+/* Number of kernel launches issued by this library on the calling thread so far. */
+uint64_t b200q_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,189 @@
+// C-ABI entry points of libb200q.so: argument checks, kernel selection, scratch layout.
+//
+// Kernel selection for b200q_qmm (the role of QuantizedMatmul::eval_gpu's dispatch,
+// mlx/backend/cuda/quantized/quantized.cpp:106-136):
+//   bf16, transpose, M <= 16, K % 128 == 0            -> qmv_mma     (HBM-bound decode)
+//   (B200Q_QMV_IMPL=bulk: 4-bit, K % 512 == 0         -> qmv_bulk, the bulk-copy staged variant)
+//   bf16, transpose, M  > 16, K % 128 == 0, N % 8 == 0 -> qmm_tcgen05 (TMA + tcgen05 + TMEM)
+//   everything else                                   -> qmm_generic
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200q {
+
+namespace {
+thread_local char g_err[512] = "";
+thread_local uint64_t g_launches = 0;
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void count_launch(int n) { g_launches += (uint64_t)n; }
+
+namespace {
+
+enum class Path { QmvBulk, Qmv, Tc, Generic };
+
+int check_qmm_args(const char* tag, const QmmArgs& a) {
+  if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[%s] Only real floating types are supported (dtype code %d).", tag, a.dtype);
+  if (!valid_group(a.group))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[%s] Quantization group size must be 32, 64 or 128 (got %d).", tag, a.group);
+  if (!valid_bits(a.bits))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[%s] Quantization bits must be 2, 3, 4, 5, 6 or 8 (got %d).", tag, a.bits);
+  if (a.batch < 0 || a.M < 0 || a.N < 0 || a.K < 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[%s] negative dimension.", tag);
+  // The quantized axis is the last axis of the stored W: K if transposed, N otherwise.
+  const int64_t qaxis = a.transpose ? a.K : a.N;
+  if (qaxis % a.group != 0 || (qaxis * a.bits) % 32 != 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT,
+                "[%s] The shapes of the weight and scales are incompatible based on bits and group_size: "
+                "quantized axis %lld with group_size=%d and bits=%d", tag, (long long)qaxis, a.group, a.bits);
+  if (a.M > INT32_MAX || a.N > INT32_MAX || a.K > INT32_MAX)
+    return fail(B200Q_ERR_UNSUPPORTED, "[%s] No implementation for problem shape: dimension exceeds 2^31-1.", tag);
+  return B200Q_OK;
+}
+
+// B200Q_QMV_IMPL=bulk|mma forces one of the two decode kernels (testing and tuning).
+int qmv_override() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_QMV_IMPL");
+    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : 0));
+  }
+  return v;
+}
+
+Path choose(const QmmArgs& a) {
+  const int ov = qmv_override();
+  // The register-path kernel is currently the faster of the two decode kernels.
+  if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
+  if (qmv_mma_supported(a)) return Path::Qmv;
+  if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
+  if (qmm_tc_supported(a)) return Path::Tc;
+  return Path::Generic;
+}
+
+QmmArgs make_args(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* y, int dtype,
+                  int64_t batch, int64_t M, int64_t N, int64_t K, int group, int bits, int transpose,
+                  int64_t w_batch_stride, void* ws, size_t ws_bytes) {
+  QmmArgs a{};
+  a.x = x; a.wq = wq; a.scales = scales; a.biases = biases; a.y = y;
+  a.dtype = dtype;
+  a.group = group; a.bits = bits;
+  a.transpose = transpose != 0;
+  a.w_batched = w_batch_stride != 0 && batch > 1;
+  // A weight matrix shared by all batches: fold the batch into M.
+  if (a.w_batched) { a.batch = batch; a.M = M; } else { a.batch = 1; a.M = batch * M; }
+  a.N = N; a.K = K;
+  a.ws = ws; a.ws_bytes = ws_bytes;
+  return a;
+}
+
+int run_qmm(const QmmArgs& a, cudaStream_t st) {
+  if (a.batch == 0 || a.M == 0 || a.N == 0) return B200Q_OK;
+  if (a.K == 0) {
+    B200Q_CUDA_OK(cudaMemsetAsync(a.y, 0, (size_t)a.batch * a.M * a.N * dtype_size(a.dtype), st));
+    return B200Q_OK;
+  }
+  if (!a.x || !a.wq || !a.scales || !a.biases || !a.y)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null pointer");
+  switch (choose(a)) {
+    case Path::QmvBulk: return qmv_bulk(a, st);
+    case Path::Qmv: return qmv_mma(a, st);
+    case Path::Tc: return qmm_tc(a, st);
+    default: return qmm_generic(a, st);
+  }
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_version(void) { return B200Q_VERSION; }
+extern "C" const char* b200q_last_error(void) { return g_err; }
+extern "C" uint64_t b200q_launch_count(void) { return g_launches; }
+
+extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                            int group_size, int bits, int transpose) {
+  // Sized for whichever kernel may be selected for this shape, for any pointer alignment.
+  QmmArgs a = make_args(nullptr, nullptr, nullptr, nullptr, nullptr, dtype, batch, M, N, K, group_size, bits,
+                        transpose, 0, nullptr, 0);
+  if (!valid_group(group_size) || !valid_bits(bits) || N <= 0 || K <= 0) return 0;
+  size_t need = 0;
+  size_t q = qmv_mma_workspace_bytes(a);
+  const size_t qb = qmv_bulk_workspace_bytes(a);
+  q = q > qb ? q : qb;
+  size_t t = qmm_tc_workspace_bytes(a);
+  need = q > t ? q : t;
+  return (need + 255) / 256 * 256;
+}
+
+extern "C" int b200q_qmm(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* y,
+                         int dtype, int64_t batch, int64_t M, int64_t N, int64_t K, int group_size, int bits,
+                         int transpose, int64_t w_batch_stride, void* ws, size_t ws_bytes, void* stream) {
+  QmmArgs a = make_args(x, wq, scales, biases, y, dtype, batch, M, N, K, group_size, bits, transpose,
+                        w_batch_stride, ws, ws_bytes);
+  if (int rc = check_qmm_args("quantized_matmul", a)) return rc;
+  return run_qmm(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
+                                             int group_size, int bits, int transpose) {
+  static const uint32_t aligned_dummy[4] __attribute__((aligned(16))) = {0, 0, 0, 0};
+  QmmArgs a = make_args(aligned_dummy, aligned_dummy, aligned_dummy, aligned_dummy, nullptr, dtype, batch, M, N, K,
+                        group_size, bits, transpose, 0, nullptr, 0);
+  if (check_qmm_args("quantized_matmul", a)) return "invalid";
+  switch (choose(a)) {
+    case Path::QmvBulk: return "qmv_bulk";
+    case Path::Qmv: return "qmv_mma";
+    case Path::Tc: return "qmm_tcgen05";
+    default: return "qmm_generic";
+  }
+}
+
+extern "C" int b200q_workspace_init(void* ws, size_t ws_bytes, void* stream) {
+  if (ws_bytes == 0) return B200Q_OK;
+  if (!ws) return fail(B200Q_ERR_INVALID_ARGUMENT, "[workspace_init] null workspace");
+  B200Q_CUDA_OK(cudaMemsetAsync(ws, 0, ws_bytes, static_cast<cudaStream_t>(stream)));
+  return B200Q_OK;
+}
+
+extern "C" int b200q_read_status(void* ws, size_t ws_bytes, void* stream, uint32_t status[4]) {
+  if (!ws || ws_bytes < kStatusBytes || !status)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[read_status] workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* p = static_cast<char*>(ws) + ws_bytes - kStatusBytes;
+  B200Q_CUDA_OK(cudaMemcpyAsync(status, p, kStatusBytes, cudaMemcpyDeviceToHost, st));
+  B200Q_CUDA_OK(cudaMemsetAsync(p, 0, kStatusBytes, st));
+  B200Q_CUDA_OK(cudaStreamSynchronize(st));
+  return B200Q_OK;
+}
+
+extern "C" int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* wq, const void* scales,
+                              const void* biases, void* y_dev, void* y_host, int dtype, int64_t M, int64_t N,
+                              int64_t K, int group_size, int bits, int transpose, void* ws, size_t ws_bytes,
+                              void* stream) {
+  QmmArgs a = make_args(x_dev, wq, scales, biases, y_dev, dtype, 1, M, N, K, group_size, bits, transpose, 0, ws,
+                        ws_bytes);
+  if (int rc = check_qmm_args("quantized_matmul", a)) return rc;
+  if (!x_host || !y_host || !x_dev || !y_dev)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null host/staging pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t es = dtype_size(dtype);
+  B200Q_CUDA_OK(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * es, cudaMemcpyHostToDevice, st));
+  if (int rc = run_qmm(a, st)) return rc;
+  B200Q_CUDA_OK(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * es, cudaMemcpyDeviceToHost, st));
+  return B200Q_OK;
+}

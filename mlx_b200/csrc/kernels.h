@@ -1,0 +1,72 @@
+// Internal interface between the C-ABI dispatch layer (api.cu) and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace b200q {
+
+struct QmmArgs {
+  const void* x;
+  const uint32_t* wq;
+  const void* scales;
+  const void* biases;
+  void* y;
+  int dtype;
+  int64_t batch;  // independent problems (grid z); 1 when W is shared and x is flattened
+  int64_t M, N, K;
+  int group, bits;
+  bool transpose;
+  bool w_batched;  // wq/scales/biases hold `batch` matrices
+  void* ws;
+  size_t ws_bytes;
+};
+
+// Grouped (mixture-of-experts) problem: rows of x sorted by expert, one segment per
+// expert.  All arrays live on the device and are produced by the sort kernels.
+struct GroupedArgs {
+  const void* x_sorted;        // [n_rows, K] activations gathered in expert order
+  const uint32_t* wq;          // [E, N, K*bits/32]
+  const void* scales;          // [E, N, K/g]
+  const void* biases;
+  void* y;                     // [n_rows_out, N]; row of sorted position p is dst_row[p]
+  const int32_t* seg_start;    // [E+1] first sorted row of each expert
+  const int32_t* dst_row;      // [n_rows] destination row in y of each sorted row
+  int dtype;
+  int64_t n_rows, E, N, K;
+  int group, bits;
+  void* ws;
+  size_t ws_bytes;
+};
+
+// Per-problem operand selection of the gather form: problem i of `batch` multiplies
+// x[lhs[i]] with w[rhs[i]].  Indices are range-checked on the device against
+// x_batch / n_mats; a bad index zeroes its output and sets status[0].
+struct GatherIdx {
+  const uint32_t* lhs;
+  const uint32_t* rhs;
+  uint32_t x_batch, n_mats;
+  uint32_t* status;
+};
+
+// qmm_generic.cu
+int qmm_generic(const QmmArgs& a, cudaStream_t st, const GatherIdx* gi = nullptr);
+
+// qmv_mma.cu : decode path, M <= 16 rows of x against W^T (transpose only, bf16)
+bool qmv_mma_supported(const QmmArgs& a);
+size_t qmv_mma_workspace_bytes(const QmmArgs& a);
+int qmv_mma(const QmmArgs& a, cudaStream_t st);
+
+// qmv_bulk.cu : decode path for 4-bit weights (bulk-copy staged, exact factorised form)
+bool qmv_bulk_supported(const QmmArgs& a);
+size_t qmv_bulk_workspace_bytes(const QmmArgs& a);
+int qmv_bulk(const QmmArgs& a, cudaStream_t st);
+
+// qmm_tcgen05.cu : prefill path (TMA + tcgen05 + TMEM), transpose only, bf16
+bool qmm_tc_supported(const QmmArgs& a);
+size_t qmm_tc_workspace_bytes(const QmmArgs& a);
+int qmm_tc(const QmmArgs& a, cudaStream_t st);
+
+}  // namespace b200q

@@ -1,0 +1,321 @@
+"""Host-side mirror of the reference operator front-end for the affine quantized path.
+
+Same names, argument meaning and error behaviour as ``mlx.core.quantize``,
+``dequantize``, ``quantized_matmul`` and ``gather_qmm`` (reference: mlx/ops.cpp:4784-4834
+quantized_matmul, :5208-5245 quantize, :5465-5517 dequantize, :5553-5629 gather_qmm;
+validation helpers :110-181, :4704-4754).  Arrays are ``torch`` CUDA tensors: torch only
+supplies device memory and streams, every computation is a call into libb200q.so.
+Invalid arguments raise ``ValueError`` (the reference's std::invalid_argument).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_MODES = ("affine", "mxfp4", "mxfp8", "nvfp4")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(tag: str, *ts: torch.Tensor) -> torch.device:
+    dev = ts[0].device
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError(f"[{tag}] tensors must live on a CUDA device: there is no CPU fallback")
+        if t.device != dev:
+            raise ValueError(f"[{tag}] all tensors must be on the same device")
+    return dev
+
+
+def _as_u32(w: torch.Tensor, tag: str) -> torch.Tensor:
+    if w.dtype == torch.uint32:
+        return w
+    raise ValueError(f"[{tag}] The weight matrix should be uint32 but received {w.dtype}")
+
+
+class _Workspaces:
+    """One zero-initialised scratch buffer per (device, stream); it only grows."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, dev: torch.device, nbytes: int) -> torch.Tensor:
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            with torch.cuda.device(dev):
+                buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=dev)
+            self._bufs[key] = buf
+        return buf
+
+
+_workspaces = _Workspaces()
+
+
+def _mode_params(mode: str, group_size, bits, tag: str) -> Tuple[int, int]:
+    if mode not in _MODES:
+        raise ValueError(f"[{tag}] Invalid quantization mode '{mode}'.")
+    if mode != "affine":
+        raise NotImplementedError(f"[{tag}] only the affine mode is built; '{mode}' is out of scope")
+    return (64 if group_size is None else int(group_size), 4 if bits is None else int(bits))
+
+
+def _validate_mode_with_type(tag, scales, biases, out_type):
+    # mlx/ops.cpp:4704-4754
+    if out_type is not None and not out_type.is_floating_point:
+        raise ValueError(f"[{tag}] Only real floating types are supported but output dtype == {out_type}.")
+    if biases is None:
+        raise ValueError(f"[{tag}] Biases must be provided for affine quantization.")
+    dtype = torch.promote_types(scales.dtype, biases.dtype)
+    if not dtype.is_floating_point:
+        raise ValueError(
+            f"[{tag}] Only real floating types are supported but scales.dtype() == {scales.dtype} "
+            f"and biases.dtype() == {biases.dtype}."
+        )
+    return out_type if out_type is not None else dtype
+
+
+def _validate_quantized_input(tag, w, scales, group_size, bits, biases):
+    # mlx/ops.cpp:110-150
+    _as_u32(w, tag)
+    if biases is not None and scales.shape != biases.shape:
+        raise ValueError(
+            f"[{tag}] Scales and biases should have the same shape. Received scales with shape "
+            f"{tuple(scales.shape)} and biases with {tuple(biases.shape)}"
+        )
+    if w.ndim < 2 or scales.ndim != w.ndim or tuple(w.shape[:-2]) != tuple(scales.shape[:-2]):
+        raise ValueError(
+            f"[{tag}] Weight and scales should have the same batch shape. Received weight with shape "
+            f"{tuple(w.shape)}, scales with {tuple(scales.shape)}."
+        )
+    if w.shape[-1] * 32 // bits != scales.shape[-1] * group_size:
+        raise ValueError(
+            f"[{tag}] The shapes of the weight and scales are incompatible based on bits and group_size. "
+            f"w.shape() == {tuple(w.shape)} and scales.shape() == {tuple(scales.shape)} "
+            f"with group_size={group_size} and bits={bits}"
+        )
+
+
+def _extract_dims(tag, x, w, scales, biases, transpose, group_size, bits):
+    # mlx/ops.cpp:152-181
+    _validate_quantized_input(tag, w, scales, group_size, bits, biases)
+    if x.ndim < 1:
+        raise ValueError(f"[{tag}] x must have at least one dimension")
+    x_inner = x.shape[-1]
+    w_inner = w.shape[-1] * 32 // bits if transpose else w.shape[-2]
+    w_outer = w.shape[-2] if transpose else w.shape[-1] * 32 // bits
+    if w_inner != x_inner:
+        raise ValueError(
+            f"[{tag}] Last dimension of first input with shape (..., {x_inner}) does not match the expanded "
+            f"quantized matrix ({w_inner}, {w_outer}) computed from shape {tuple(w.shape)} with "
+            f"group_size={group_size}, bits={bits} and transpose={transpose}"
+        )
+    return w_inner, w_outer
+
+
+# --------------------------------------------------------------------------- quantize
+def quantize(w: torch.Tensor, group_size: Optional[int] = None, bits: Optional[int] = None,
+             mode: str = "affine"):
+    """-> (w_q uint32 [..., K*bits/32], scales [..., K/g], biases [..., K/g]); mlx/ops.cpp:5208."""
+    group_size, bits = _mode_params(mode, group_size, bits, "quantize")
+    if not w.dtype.is_floating_point or w.dtype not in _DT:
+        raise ValueError(f"[quantize] Only real floating types can be quantized but w has type {w.dtype}.")
+    if w.ndim < 2:
+        raise ValueError(
+            f"[quantize] The matrix to be quantized must have at least 2 dimension but it has only {w.ndim}."
+        )
+    if group_size not in (32, 64, 128):
+        raise ValueError(
+            f"[quantize] The requested group size {group_size} is not supported. "
+            "The supported group sizes are 32, 64, and 128."
+        )
+    if bits < 2 or bits > 8 or bits == 7:
+        raise ValueError(
+            f"[quantize] The requested number of bits {bits} is not supported. "
+            "The supported bits are 2, 3, 4, 5, 6 and 8."
+        )
+    if w.shape[-1] % group_size != 0:
+        raise ValueError(
+            f"[quantize] The last dimension of the matrix needs to be divisible by the quantization group "
+            f"size {group_size}. However the provided matrix has shape {tuple(w.shape)}"
+        )
+    dev = _require_cuda("quantize", w)
+    w = w.contiguous()
+    K = w.shape[-1]
+    rows = w.numel() // K if K else 0
+    lead = tuple(w.shape[:-1])
+    with torch.cuda.device(dev):
+        wq = torch.empty(lead + (K * bits // 32,), dtype=torch.uint32, device=dev)
+        scales = torch.empty(lead + (K // group_size,), dtype=w.dtype, device=dev)
+        biases = torch.empty_like(scales)
+        rc = _lib.load().b200q_quantize(_ptr(w), _DT[w.dtype], rows, K, group_size, bits, _ptr(wq),
+                                        _ptr(scales), _ptr(biases), _stream(w))
+    _lib.check(rc)
+    return wq, scales, biases
+
+
+def dequantize(w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor] = None,
+               group_size: Optional[int] = None, bits: Optional[int] = None, mode: str = "affine",
+               dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """mlx/ops.cpp:5465-5517 (+ affine_dequantize :5258-5340)."""
+    group_size, bits = _mode_params(mode, group_size, bits, "dequantize")
+    out_type = _validate_mode_with_type("dequantize", scales, biases, dtype)
+    if bits <= 0:
+        raise ValueError(f"[dequantize] Invalid value for bits: {bits}")
+    if group_size <= 0:
+        raise ValueError(f"[dequantize] Invalid value for group_size: {group_size}")
+    if w.dtype != torch.uint32:
+        raise ValueError("[dequantize] The matrix should be given as a uint32")
+    if w.ndim < 2:
+        raise ValueError(
+            f"[dequantize] The matrix to be dequantized must have at least 2 dimension but it has only {w.ndim}."
+        )
+    if (w.ndim != scales.ndim or w.ndim != biases.ndim or tuple(w.shape[:-1]) != tuple(scales.shape[:-1])
+            or tuple(w.shape[:-1]) != tuple(biases.shape[:-1])):
+        raise ValueError("[dequantize] Shape of scales and biases does not match the matrix")
+    K = w.shape[-1] * 32 // bits
+    if K != scales.shape[-1] * group_size or scales.shape != biases.shape:
+        raise ValueError(
+            "[dequantize] Shape of scales and biases does not match the matrix given the quantization "
+            f"parameters. Provided matrix of shape {tuple(w.shape)} and scales/biases of shape "
+            f"{tuple(scales.shape)} with group_size={group_size} and bits={bits}."
+        )
+    if scales.dtype not in _DT or scales.dtype != biases.dtype:
+        ct = torch.promote_types(scales.dtype, biases.dtype)
+        scales, biases = scales.to(ct), biases.to(ct)
+    dev = _require_cuda("dequantize", w, scales, biases)
+    w, scales, biases = w.contiguous(), scales.contiguous(), biases.contiguous()
+    rows = w.numel() // w.shape[-1] if w.shape[-1] else 0
+    with torch.cuda.device(dev):
+        out = torch.empty(tuple(w.shape[:-1]) + (K,), dtype=scales.dtype, device=dev)
+        rc = _lib.load().b200q_dequantize(_ptr(w), _ptr(scales), _ptr(biases), _DT[scales.dtype], rows, K,
+                                          group_size, bits, _ptr(out), _stream(w))
+    _lib.check(rc)
+    return out if out.dtype == out_type else out.to(out_type)
+
+
+# ------------------------------------------------------------------- quantized_matmul
+def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
+                     biases: Optional[torch.Tensor] = None, transpose: bool = True,
+                     group_size: Optional[int] = None, bits: Optional[int] = None,
+                     mode: str = "affine") -> torch.Tensor:
+    """mlx/ops.cpp:4784-4834.  x [..., M, K] (or [K]); w [..., N, K*bits/32] when transposed."""
+    group_size, bits = _mode_params(mode, group_size, bits, "quantized_matmul")
+    dtype = _validate_mode_with_type("quantized_matmul", scales, biases, None)
+    _, w_outer = _extract_dims("quantized_matmul", x, w, scales, biases, transpose, group_size, bits)
+    dtype = torch.promote_types(x.dtype, dtype)
+    if not dtype.is_floating_point or dtype not in _DT:
+        raise ValueError(f"[quantized_matmul] Only real floating types are supported but x.dtype() == {x.dtype}.")
+    dev = _require_cuda("quantized_matmul", x, w, scales, biases)
+    x, scales, biases = x.to(dtype), scales.to(dtype), biases.to(dtype)
+
+    vector = x.ndim == 1
+    if vector:
+        x = x.unsqueeze(0)
+    K = x.shape[-1]
+    M = x.shape[-2]
+    if x.ndim > 2 and w.ndim > 2:
+        # both batched: broadcast the batch dimensions (mlx/ops.cpp:4823-4825)
+        bshape = torch.broadcast_shapes(x.shape[:-2], w.shape[:-2])
+        x = x.expand(bshape + x.shape[-2:]).contiguous()
+        w = w.expand(bshape + w.shape[-2:]).contiguous()
+        scales = scales.expand(bshape + scales.shape[-2:]).contiguous()
+        biases = biases.expand(bshape + biases.shape[-2:]).contiguous()
+        batch, w_stride, out_lead = x.numel() // max(M * K, 1), 1, tuple(bshape)
+    elif w.ndim > 2:
+        # 2-D x against a stack of matrices
+        bshape = tuple(w.shape[:-2])
+        x = x.expand(bshape + x.shape[-2:]).contiguous()
+        w, scales, biases = w.contiguous(), scales.contiguous(), biases.contiguous()
+        batch, w_stride, out_lead = w.numel() // max(w.shape[-1] * w.shape[-2], 1), 1, bshape
+    else:
+        x, w, scales, biases = x.contiguous(), w.contiguous(), scales.contiguous(), biases.contiguous()
+        out_lead = tuple(x.shape[:-2])
+        batch, w_stride = (x.numel() // max(M * K, 1) if M * K else 0), 0
+        if M * K == 0:
+            batch = 1
+            for d in out_lead:
+                batch *= d
+    N = w_outer
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        y = torch.empty(out_lead + (M, N), dtype=dtype, device=dev)
+        need = lib.b200q_qmm_workspace_bytes(_DT[dtype], batch, M, N, K, group_size, bits, int(transpose))
+        ws = _workspaces.get(dev, need)
+        rc = lib.b200q_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(y), _DT[dtype], batch, M, N, K,
+                           group_size, bits, int(transpose), w_stride, _ptr(ws), ws.numel(), _stream(x))
+    _lib.check(rc)
+    return y.squeeze(-2) if vector else y
+
+
+# -------------------------------------------------------------------------- gather_qmm
+def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Tensor] = None,
+               lhs_indices: Optional[torch.Tensor] = None, rhs_indices: Optional[torch.Tensor] = None,
+               transpose: bool = True, group_size: Optional[int] = None, bits: Optional[int] = None,
+               mode: str = "affine", sorted_indices: bool = False) -> torch.Tensor:
+    """mlx/ops.cpp:5553-5629.  out shape = broadcast(lhs, rhs).shape + [M, N]."""
+    if lhs_indices is None and rhs_indices is None:
+        return quantized_matmul(x, w, scales, biases, transpose, group_size, bits, mode)
+    group_size, bits = _mode_params(mode, group_size, bits, "gather_qmm")
+    out_type = _validate_mode_with_type("gather_qmm", scales, biases, None)
+    _, w_outer = _extract_dims("gather_qmm", x, w, scales, biases, transpose, group_size, bits)
+    out_type = torch.promote_types(x.dtype, out_type)
+    if not out_type.is_floating_point or out_type not in _DT:
+        raise ValueError(f"[gather_qmm] Only real floating types are supported but x.dtype() == {x.dtype}.")
+    if x.ndim < 2:
+        raise ValueError("[gather_qmm] x must have at least two dimensions")
+    for idx, name in ((lhs_indices, "lhs_indices"), (rhs_indices, "rhs_indices")):
+        if idx is not None and (idx.dtype.is_floating_point or idx.dtype == torch.bool):
+            raise ValueError(f"[gather_qmm] Got {name} with invalid dtype. Indices must be integral.")
+    dev = _require_cuda("gather_qmm", x, w, scales, biases)
+
+    def default_idx(t):  # indices_or_default, mlx/ops.cpp:79-108
+        shape = tuple(t.shape[:-2])
+        n = 1
+        for d in shape:
+            n *= d
+        return torch.arange(n, dtype=torch.int64, device=dev).reshape(shape)
+
+    lhs = default_idx(x) if lhs_indices is None else lhs_indices.to(device=dev, dtype=torch.int64)
+    rhs = default_idx(w) if rhs_indices is None else rhs_indices.to(device=dev, dtype=torch.int64)
+    lhs, rhs = torch.broadcast_tensors(lhs, rhs)
+    idx_shape = tuple(lhs.shape)
+    lhs32 = lhs.contiguous().reshape(-1).to(torch.int32)  # bit pattern of uint32 indices
+    rhs32 = rhs.contiguous().reshape(-1).to(torch.int32)
+
+    x, scales, biases = x.to(out_type).contiguous(), scales.to(out_type).contiguous(), biases.to(out_type).contiguous()
+    w = w.contiguous()
+    M, K = x.shape[-2], x.shape[-1]
+    x_batch = x.numel() // max(M * K, 1) if M * K else 0
+    E = w.numel() // max(w.shape[-1] * w.shape[-2], 1) if w.shape[-1] * w.shape[-2] else 0
+    N = w_outer
+    n_idx = lhs32.numel()
+    flags = (1 if (sorted_indices and rhs_indices is None) else 0) | (2 if (sorted_indices and lhs_indices is None) else 0)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        y = torch.empty(idx_shape + (M, N), dtype=out_type, device=dev)
+        need = lib.b200q_gather_qmm_workspace_bytes(_DT[out_type], n_idx, x_batch, E, M, N, K, group_size, bits,
+                                                    int(transpose))
+        ws = _workspaces.get(dev, need)
+        rc = lib.b200q_gather_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(lhs32), _ptr(rhs32), n_idx,
+                                  _ptr(y), _DT[out_type], x_batch, E, M, N, K, group_size, bits, int(transpose),
+                                  flags, _ptr(ws), ws.numel(), _stream(x))
+    _lib.check(rc)
+    return y
+
+
+def qmm_kernel_name(dtype: torch.dtype, M: int, N: int, K: int, group_size: int = 64, bits: int = 4,
+                    transpose: bool = True, batch: int = 1) -> str:
+    """Which kernel family quantized_matmul launches for this problem."""
+    return _lib.load().b200q_qmm_kernel_name(_DT[dtype], batch, M, N, K, group_size, bits, int(transpose)).decode()

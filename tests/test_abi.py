@@ -1,0 +1,73 @@
+"""The C-ABI library loads without a GPU, exports every symbol include/b200q.h declares,
+and rejects invalid arguments on the host before touching CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from mlx_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200q_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    syms = declared_symbols()
+    assert syms, "no declarations parsed"
+    assert sorted(_lib.SIGNATURES) == syms
+
+
+def test_library_exports_all_symbols():
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for s in declared_symbols():
+        assert hasattr(lib, s), s
+    assert _lib.load().b200q_version() == 1
+
+
+@pytest.mark.parametrize("group,bits,K,code", [
+    (48, 4, 256, _lib.ERR_INVALID_ARGUMENT),
+    (64, 7, 256, _lib.ERR_INVALID_ARGUMENT),
+    (64, 1, 256, _lib.ERR_INVALID_ARGUMENT),
+    (64, 4, 96, _lib.ERR_INVALID_ARGUMENT),
+])
+def test_quantize_rejects_on_host(group, bits, K, code):
+    lib = _lib.load()
+    rc = lib.b200q_quantize(None, _lib.BF16, 4, K, group, bits, None, None, None, None)
+    assert rc == code
+    assert _lib.last_error()
+    with pytest.raises(ValueError):
+        _lib.check(rc)
+
+
+def test_qmm_rejects_on_host():
+    lib = _lib.load()
+    bad = [
+        dict(dtype=7), dict(group=16), dict(bits=7), dict(K=100), dict(M=-1),
+    ]
+    for kw in bad:
+        a = dict(dtype=_lib.BF16, M=4, N=64, K=256, group=64, bits=4)
+        a.update(kw)
+        rc = lib.b200q_qmm(None, None, None, None, None, a["dtype"], 1, a["M"], a["N"], a["K"], a["group"],
+                           a["bits"], 1, 0, None, 0, None)
+        assert rc == _lib.ERR_INVALID_ARGUMENT, kw
+    # empty problems succeed without touching the device
+    assert lib.b200q_qmm(None, None, None, None, None, _lib.BF16, 1, 0, 64, 256, 64, 4, 1, 0, None, 0, None) == 0
+    assert lib.b200q_quantize(None, _lib.F32, 0, 256, 64, 4, None, None, None, None) == 0
+
+
+def test_kernel_selection_names():
+    lib = _lib.load()
+    name = lambda M, N, K, dt=_lib.BF16, tr=1, bits=4, g=64: lib.b200q_qmm_kernel_name(dt, 1, M, N, K, g, bits, tr).decode()
+    assert name(1, 4096, 4096) in ("qmv_mma", "qmv_bulk")
+    assert name(16, 14336, 4096) in ("qmv_mma", "qmv_bulk")
+    assert name(16, 14336, 4096, bits=3) == "qmv_mma"
+    assert name(16, 14336, 4096, dt=_lib.F32) == "qmm_generic"
+    assert name(16, 4096, 4096, tr=0) == "qmm_generic"
+    assert name(4, 100, 96, g=32) == "qmm_generic"
+    assert lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, 16, 14336, 4096, 64, 4, 1) > 14336 * 64

@@ -1,0 +1,167 @@
+"""GPU parity of quantized_matmul against the reference's float instantiation fed the
+same (exactly representable) inputs.  Tolerance (bf16/f16 outputs):
+|y - y_ref| <= 1e-2*|y_ref| + 1e-2*rms(y_ref); float32 outputs: 1e-4 on the same form."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mlx_b200 as mb
+import oracle as O
+from util import col_scale, from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "affine_golden.npz")
+REL = {"f32": 1e-4, "f16": 1e-2, "bf16": 1e-2}
+
+
+def run_case(dtype, M, N, K, g, bits, transpose=True, seed=0, expect_kernel=None):
+    wshape = (N, K) if transpose else (K, N)
+    w = make_w(100 + seed, wshape, dtype)
+    wq, s, b = O.quantize(w, g, bits, dtype)
+    x = make_x(200 + seed, (M, K), dtype)
+    ref = O.qmm_f32_from(x, wq, s, b, dtype, transpose=transpose, group_size=g, bits=bits)
+    if expect_kernel is not None:
+        assert mb.qmm_kernel_name(torch.bfloat16 if dtype == "bf16" else (torch.float16 if dtype == "f16" else torch.float32),
+                                  M, N, K, g, bits, transpose) in expect_kernel
+    y = mb.quantized_matmul(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype),
+                            transpose=transpose, group_size=g, bits=bits)
+    assert tuple(y.shape) == (M, N)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), ref, REL[dtype])
+    assert ok, f"max err / max|ref| = {rel:.3e}"
+    return rel
+
+
+@pytest.mark.parametrize("dtype", ("f32", "f16", "bf16"))
+@pytest.mark.parametrize("g", (32, 64, 128))
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+def test_golden_qmm(dtype, g, bits):
+    gold = np.load(GOLDEN)
+    t = f"{dtype}_g{g}_b{bits}"
+    args = (u32_to_torch(gold[f"{t}/wq"]), to_torch(gold[f"{t}/s"], dtype), to_torch(gold[f"{t}/b"], dtype))
+    y = mb.quantized_matmul(to_torch(gold[f"{t}/x"], dtype), *args, transpose=True, group_size=g, bits=bits)
+    # the golden weights hold rows of very different magnitude (edge-case groups): scale the
+    # absolute term per output column
+    cs = col_scale(gold[f"{t}/wq"], gold[f"{t}/s"], gold[f"{t}/b"], gold[f"{t}/x"], dtype, g, bits)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), gold[f"{t}/y32"], REL[dtype], cs[None, :])
+    assert ok, rel
+    # transpose=False on the same packed array read as [K=8, N=256]
+    yn = mb.quantized_matmul(to_torch(gold[f"{t}/xn"], dtype), *args, transpose=False, group_size=g, bits=bits)
+    refn = O.qmm_f32_from(gold[f"{t}/xn"], gold[f"{t}/wq"], gold[f"{t}/s"], gold[f"{t}/b"], dtype,
+                          transpose=False, group_size=g, bits=bits)
+    ok, rel = qmm_close(O.to_f32(from_torch(yn), dtype), refn, REL[dtype])
+    assert ok, rel
+
+
+# ---- decode path (mma.sync GEMV / skinny GEMM) ---------------------------------------
+@pytest.mark.parametrize("bits", (2, 3, 4, 5, 6, 8))
+@pytest.mark.parametrize("g", (32, 64, 128))
+@pytest.mark.parametrize("M", (1, 3, 8, 9, 16))
+def test_qmv_all_widths(bits, g, M):
+    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_mma", "qmv_bulk"))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 14336, 4096), (7, 67, 256), (2, 8, 128), (16, 1000, 2048),
+                                   (5, 28672, 8192), (13, 4104, 4096), (16, 24, 128)])
+def test_qmv_shapes_4bit(M, N, K):
+    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_mma", "qmv_bulk"))
+
+
+def test_qmv_repeated_calls_reuse_scratch():
+    """The scratch counters and partial sums must be left clean by every call."""
+    dtype, M, N, K = "bf16", 16, 14336, 4096
+    w = make_w(1, (N, K), dtype)
+    wq, s, b = O.quantize(w, 64, 4, dtype)
+    args = (u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype))
+    x = to_torch(make_x(2, (M, K), dtype), dtype)
+    y0 = mb.quantized_matmul(x, *args)
+    for _ in range(5):
+        y = mb.quantized_matmul(x, *args)
+        assert torch.equal(y.view(torch.int16), y0.view(torch.int16)) or torch.allclose(y.float(), y0.float(), rtol=2e-2, atol=1e-2)
+    ref = O.qmm_f32_from(from_torch(x), wq, s, b, dtype, transpose=True, group_size=64, bits=4)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), ref)
+    assert ok, rel
+
+
+# ---- generic path ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ("f32", "f16"))
+@pytest.mark.parametrize("transpose", (True, False))
+@pytest.mark.parametrize("bits,g", [(2, 128), (4, 64), (8, 32), (3, 64), (5, 32), (6, 128)])
+@pytest.mark.parametrize("M", (8, 33))
+def test_generic_shapes(dtype, transpose, bits, g, M):
+    # shapes of the reference's test_qmm (python/tests/test_quantized.py:288-323)
+    run_case(dtype, M, 256, 128, g, bits, transpose=transpose, seed=M)
+
+
+@pytest.mark.parametrize("transpose", (True, False))
+def test_bf16_no_transpose_and_ragged(transpose):
+    run_case("bf16", 33, 384, 256, 64, 4, transpose=transpose, seed=3)
+    run_case("bf16", 5, 96, 160, 32, 8, transpose=transpose, seed=4)
+
+
+def test_batched_x_and_vector_x():
+    dtype = "bf16"
+    w = make_w(5, (256, 512), dtype)
+    wq, s, b = O.quantize(w, 64, 4, dtype)
+    x = make_x(6, (3, 4, 512), dtype)
+    y = mb.quantized_matmul(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype))
+    assert tuple(y.shape) == (3, 4, 256)
+    ref = O.qmm_f32_from(x.reshape(12, 512), wq, s, b, dtype, transpose=True, group_size=64, bits=4)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype).reshape(12, 256), ref)
+    assert ok, rel
+    yv = mb.quantized_matmul(to_torch(x[0, 0], dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype))
+    assert tuple(yv.shape) == (256,)
+    ok, rel = qmm_close(O.to_f32(from_torch(yv), dtype), ref[0])
+    assert ok, rel
+
+
+def test_batched_weights():
+    dtype = "f32"
+    w = make_w(7, (3, 64, 128), dtype)
+    wq, s, b = O.quantize(w, 32, 4, dtype)
+    x = make_x(8, (3, 5, 128), dtype)
+    y = mb.quantized_matmul(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype), group_size=32)
+    for i in range(3):
+        ref = O.qmm(x[i], wq[i], s[i], b[i], True, 32, 4, dtype)
+        ok, rel = qmm_close(from_torch(y[i]), ref, 1e-4)
+        assert ok, rel
+
+
+def test_mixed_dtype_promotes_to_float32():
+    # bf16 x with float32 scales promotes to float32 (mlx/ops.cpp:4803-4818)
+    w = make_w(9, (64, 128), "f32")
+    wq, s, b = O.quantize(w, 64, 4, "f32")
+    x = make_x(10, (4, 128), "bf16")
+    y = mb.quantized_matmul(to_torch(x, "bf16"), u32_to_torch(wq), to_torch(s, "f32"), to_torch(b, "f32"))
+    assert y.dtype == torch.float32
+    ref = O.qmm(O.to_f32(x, "bf16"), wq, s, b, True, 64, 4, "f32")
+    ok, rel = qmm_close(from_torch(y), ref, 1e-4)
+    assert ok, rel
+
+
+def test_qmv_bulk_variant_in_subprocess():
+    """The bulk-copy staged decode kernel is selected with B200Q_QMV_IMPL=bulk; run a few
+    shapes through it in a child process (the override is read once per process)."""
+    import subprocess
+    import sys
+    code = r'''
+import sys
+sys.path.insert(0, "tests")
+import torch, oracle as O, mlx_b200 as mb
+from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch
+for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048, 32), (13, 4104, 4096, 128), (5, 520, 8192, 64)]:
+    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4) == "qmv_bulk"
+    wq, s, b = O.quantize(make_w(N, (N, K), "bf16"), g, 4, "bf16")
+    x = make_x(M, (M, K), "bf16")
+    ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
+    for _ in range(2):
+        y = mb.quantized_matmul(to_torch(x, "bf16"), u32_to_torch(wq), to_torch(s, "bf16"), to_torch(b, "bf16"), group_size=g, bits=4)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), "bf16"), ref)
+    assert ok, (M, N, K, g, rel)
+print("bulk-ok")
+'''
+    env = dict(os.environ, B200Q_QMV_IMPL="bulk")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "bulk-ok" in res.stdout, res.stdout + res.stderr
