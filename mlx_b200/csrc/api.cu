@@ -64,8 +64,18 @@ int qmv_override() {
   return v;
 }
 
+bool force_tc() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_FORCE_TC");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
 Path choose(const QmmArgs& a) {
   const int ov = qmv_override();
+  if (force_tc() && qmm_tc_supported(a)) return Path::Tc;  // tuning aid: tensor-memory path for any M
   // The register-path kernel is currently the faster of the two decode kernels.
   if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
   if (qmv_mma_supported(a)) return Path::Qmv;

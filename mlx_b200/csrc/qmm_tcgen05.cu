@@ -1,7 +1,473 @@
+// Prefill path: y[M, N] = x[M, K] * dequant(W[N, K])^T on the 5th-generation tensor cores.
+//
+// Replaces cu::qmm_sm80_kernel / qmm_naive_kernel of the reference
+// (mlx/backend/cuda/device/qmm_sm80.cuh:70-356, quantized/qmm/qmm.cu:20-185), which run
+// Ampere-style mma.sync code on this GPU.
+//
+// Formulation (swap-AB): the MMA computes D[128 weight rows, NT tokens] so that the
+// operand that has to be dequantised (W) is the 128-row A operand and is re-used by up
+// to 256 tokens per instruction, and the operand that streams unchanged (x) is B.
+//
+//   TMA  --packed W tile [128 rows x 64 k]-->  smem ring P
+//   8 dequant warps: one thread per weight row (= one TMEM lane): unpack 32 k with
+//        shift/lop3/prmt, apply s*q+b in bf16x2, tcgen05.st into the A ring in TMEM
+//   TMA  --x tile [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
+//   1 thread: tcgen05.mma.kind::f16 (A from TMEM, B from smem descriptors), fp32
+//        accumulator [128 lanes x NT columns] in TMEM, tcgen05.commit on mbarriers
+//   4 epilogue warps: tcgen05.ld the accumulator, round to bf16, store y (transposed)
+//
+// TMEM columns (512 allocated): [0, 256) accumulator, [256, 512) A ring of 8 stages
+// (64 k of bf16 = 32 columns each).  One CTA per SM (persistent), tiles are taken
+// round-robin; no CTA ever waits on another CTA.
+//
+// Every mbarrier wait is bounded.  When a wait expires the role sets the CTA abort
+// flag and the device status word, all roles leave their loops, TMEM is released and
+// the kernel ends normally (its results are then invalid and the host reports it).
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
+
 namespace b200q {
-bool qmm_tc_supported(const QmmArgs&) { return false; }
-size_t qmm_tc_workspace_bytes(const QmmArgs&) { return 0; }
-int qmm_tc(const QmmArgs&, cudaStream_t) { return fail(B200Q_ERR_UNSUPPORTED, "qmm_tcgen05 not built"); }
+namespace {
+
+constexpr int kTileN = 128;       // weight rows per tile (MMA M)
+constexpr int kBlockK = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
+constexpr int kStagesA = 8;       // A ring in TMEM (32 columns each)
+constexpr int kStagesB = 4;       // x tiles in shared memory
+constexpr int kStagesP = 4;       // packed W tiles in shared memory
+constexpr int kAccCols = 256;
+constexpr int kTmemCols = 512;
+constexpr int kDequantWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kThreads = 32 * (2 + kDequantWarps + kEpilogueWarps);  // 448
+constexpr uint32_t kSpinLimit = 1u << 21;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait; also gives up as soon as another role has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (i > 8) {
+      __nanosleep(32);
+      if ((i & 63) == 0 && *abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tcgen05_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand tile whose
+// rows are 128 bytes (64 bf16): 8-row groups are 1024 bytes apart (SBO), descriptor
+// version 1 (sm_100), layout type 2 = SWIZZLE_128B.  `addr` may point 32*j bytes into
+// the first row to select the j-th 16-element K slice.
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);        // start address  [0,14)
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset [32,46)
+  d |= (uint64_t)1 << 46;                        // descriptor version
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+}
+
+struct TcParams {
+  const __nv_bfloat16* scales;
+  const __nv_bfloat16* biases;
+  __nv_bfloat16* y;
+  uint32_t* status;
+  int M, N, K;
+  int NT;            // tokens per tile (multiple of 16, <= 256)
+  int n_tiles, m_tiles;
+  int group_shift;   // log2(group / 32)
+};
+
+struct __align__(8) Barriers {
+  uint64_t full_p[kStagesP], empty_p[kStagesP];
+  uint64_t full_b[kStagesB], empty_b[kStagesB];
+  uint64_t full_a[kStagesA], empty_a[kStagesA];
+  uint64_t acc_full, acc_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Unpacks 32 consecutive 4-bit fields (4 words) of one row into 16 bf16x2 registers in
+// natural k order, applying w = s*q + b (one rounding).
+__device__ __forceinline__ void dequant32_b4(const uint4 w, uint32_t s2, uint32_t b2, uint32_t (&out)[16]) {
+  constexpr uint32_t kMagic = 0x43004300u;  // (128.0, 128.0): 0x4300 | q == 128 + q
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // p[i] = (q[i], q[i+4]) as bf16 pairs
+      const uint32_t t = lop3_and_or(ws[j] >> (4 * i), 0x000F000Fu, kMagic);
+      p[i] = fma_bf16x2(sub_bf16x2(t, kMagic), s2, b2);
+    }
+    out[4 * j + 0] = __byte_perm(p[0], p[1], 0x5410);  // (w0, w1)
+    out[4 * j + 1] = __byte_perm(p[2], p[3], 0x5410);  // (w2, w3)
+    out[4 * j + 2] = __byte_perm(p[0], p[1], 0x7632);  // (w4, w5)
+    out[4 * j + 3] = __byte_perm(p[2], p[3], 0x7632);  // (w6, w7)
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+              const TcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // carve-up: [B ring: kStagesB * NT*128 B (1024-aligned)] [P ring: kStagesP * 4096 B] [barriers]
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t b_stage_bytes = (uint32_t)p.NT * 128u;
+  const uint32_t b_stage_pitch = (b_stage_bytes + 1023u) & ~1023u;
+  unsigned char* ring_b = smem;
+  unsigned char* ring_p = ring_b + (size_t)kStagesB * b_stage_pitch;
+  Barriers* bars = reinterpret_cast<Barriers*>(ring_p + (size_t)kStagesP * (kTileN * 32));
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblocks = p.K / kBlockK;
+  const int total_tiles = p.n_tiles * p.m_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStagesP; ++i) { mbar_init(smem_u32(&bars->full_p[i]), 1); mbar_init(smem_u32(&bars->empty_p[i]), kDequantWarps); }
+    for (int i = 0; i < kStagesB; ++i) { mbar_init(smem_u32(&bars->full_b[i]), 1); mbar_init(smem_u32(&bars->empty_b[i]), 1); }
+    for (int i = 0; i < kStagesA; ++i) { mbar_init(smem_u32(&bars->full_a[i]), kDequantWarps); mbar_init(smem_u32(&bars->empty_a[i]), 1); }
+    mbar_init(smem_u32(&bars->acc_full), 1);
+    mbar_init(smem_u32(&bars->acc_empty), kEpilogueWarps);
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tcgen05_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tcgen05_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tmem_acc = tmem_base;
+  const uint32_t tmem_a = tmem_base + kAccCols;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;  // k-block counter across tiles
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const int tm = tile % p.m_tiles, tn = tile / p.m_tiles;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
+          const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
+          if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) break;
+          mbar_expect_tx(smem_u32(&bars->full_p[sp]), kTileN * 32);
+          tma_load_2d(smem_u32(ring_p + sp * (kTileN * 32)), &map_w, kb * 32, tn * kTileN, smem_u32(&bars->full_p[sp]));
+          if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) break;
+          mbar_expect_tx(smem_u32(&bars->full_b[sb]), b_stage_bytes);
+          tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tm * p.NT, smem_u32(&bars->full_b[sb]));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.NT);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        if (!mbar_wait(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
+        tcgen05_fence_after();
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
+          const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
+          if (!mbar_wait(smem_u32(&bars->full_a[sa]), pa, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bars->full_b[sb]), pb, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t b_addr = smem_u32(ring_b + sb * b_stage_pitch);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / 16; ++kk) {
+            tcgen05_mma_ts(tmem_acc, tmem_a + sa * 32 + kk * 8, make_sw128_desc(b_addr + kk * 32), idesc,
+                           (kb | kk) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(smem_u32(&bars->empty_a[sa]));
+          tcgen05_commit(smem_u32(&bars->empty_b[sb]));
+        }
+        if (!ok) break;
+        tcgen05_commit(smem_u32(&bars->acc_full));
+      }
+    }
+  } else if (warp < 2 + kDequantWarps) {
+    // ------------------------------------------------------------ dequant: one thread per weight row
+    const int dq = warp - 2;
+    const int quad = warp & 3;           // TMEM lane quadrant this warp may access
+    const int half = dq >> 2;            // which 32-k half of the 64-k block
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+    const int row_groups = p.K >> (5 + p.group_shift);
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+      const int tn = tile / p.m_tiles;
+      int row = tn * kTileN + row_in_tile;
+      row = row < p.N ? row : p.N - 1;  // rows past N: packed data is zero-filled by TMA
+      const unsigned short* sc = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * row_groups;
+      const unsigned short* bi = reinterpret_cast<const unsigned short*>(p.biases) + (size_t)row * row_groups;
+      uint32_t s_next = __ldg(sc + ((half * 32) >> (5 + p.group_shift)));
+      uint32_t b_next = __ldg(bi + ((half * 32) >> (5 + p.group_shift)));
+      bool ok = true;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
+        const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
+        const uint32_t s_cur = s_next, b_cur = b_next;
+        if (kb + 1 < kblocks) {
+          const int g = ((kb + 1) * kBlockK + half * 32) >> (5 + p.group_shift);
+          s_next = __ldg(sc + g);
+          b_next = __ldg(bi + g);
+        }
+        if (!mbar_wait(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
+        const uint4 w = *reinterpret_cast<const uint4*>(ring_p + sp * (kTileN * 32) + row_in_tile * 32 + half * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
+        uint32_t vals[16];
+        dequant32_b4(w, s_cur * 0x00010001u, b_cur * 0x00010001u, vals);
+        if (!mbar_wait(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        tcgen05_st_x16(tmem_a + lane_field + sa * 32 + half * 16, vals);
+        tcgen05_wait_st();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[sa]));
+      }
+      if (!ok) break;
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quad = warp & 3;
+    const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const int tm = tile % p.m_tiles, tn = tile / p.m_tiles;
+      if (!mbar_wait(smem_u32(&bars->acc_full), tcount & 1, abort_flag)) break;
+      tcgen05_fence_after();
+      const int n = tn * kTileN + quad * 32 + lane;
+      const int m0 = tm * p.NT;
+      for (int c = 0; c < p.NT; c += 32) {
+        uint32_t v[32];
+        tcgen05_ld_x32(tmem_acc + lane_field + c, v);
+        tcgen05_wait_ld();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c + j;
+            if (c + j < p.NT && m < p.M) p.y[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+    }
+  }
+
+  // ---- teardown: everyone meets, then the allocating warp returns the tensor memory
+  tcgen05_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicMax(&p.status[0], 3u);
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tcgen05_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+int pick_nt(int64_t M) {
+  int64_t nt = (M + 15) / 16 * 16;
+  return (int)(nt > 256 ? 256 : nt);
+}
+
+size_t smem_bytes(int nt) {
+  const size_t b_pitch = ((size_t)nt * 128 + 1023) & ~size_t(1023);
+  const size_t need = 1024 + kStagesB * b_pitch + (size_t)kStagesP * kTileN * 32 + sizeof(Barriers) + 64;
+  // More than half of an SM's shared memory: guarantees one CTA per SM, so the 512-column
+  // tensor-memory allocation never has to wait for a co-resident CTA of this kernel.
+  const size_t one_per_sm = 120 * 1024;
+  return need > one_per_sm ? need : one_per_sm;
+}
+
+}  // namespace
+
+bool qmm_tc_supported(const QmmArgs& a) {
+  if (a.dtype != B200Q_BF16 || !a.transpose || a.w_batched || a.batch != 1 || a.bits != 4) return false;
+  if (a.M < 1 || a.N < 1 || a.K < kBlockK || a.K % kBlockK != 0) return false;
+  if (a.K % a.group != 0) return false;
+  // TMA: 16-byte aligned bases and row pitches (x rows: 2K bytes, packed rows: K/2 bytes)
+  if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (reinterpret_cast<uintptr_t>(a.wq) & 15)) return false;
+  if ((a.K * 2) % 16 != 0 || (a.K / 2) % 16 != 0) return false;
+  return true;
+}
+
+size_t qmm_tc_workspace_bytes(const QmmArgs&) { return kStatusBytes; }
+
+int qmm_tc(const QmmArgs& a, cudaStream_t st) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(B200Q_ERR_CUDA, "[quantized_matmul] cuTensorMapEncodeTiled is not available");
+  if (!a.ws || a.ws_bytes < kStatusBytes)
+    return fail(B200Q_ERR_WORKSPACE, "[quantized_matmul] workspace of %zu bytes required, %zu given",
+                (size_t)kStatusBytes, a.ws_bytes);
+  const int nt = pick_nt(a.M);
+  CUtensorMap map_x, map_w;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)nt};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for x failed (%d)", (int)r);
+  }
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K / 2, (cuuint64_t)a.N};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K / 2};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.wq), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for w failed (%d)", (int)r);
+  }
+  TcParams p{};
+  p.scales = (const __nv_bfloat16*)a.scales;
+  p.biases = (const __nv_bfloat16*)a.biases;
+  p.y = (__nv_bfloat16*)a.y;
+  p.status = reinterpret_cast<uint32_t*>(static_cast<char*>(a.ws) + a.ws_bytes - kStatusBytes);
+  p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+  p.NT = nt;
+  p.n_tiles = (int)((a.N + kTileN - 1) / kTileN);
+  p.m_tiles = (int)((a.M + nt - 1) / nt);
+  p.group_shift = a.group == 32 ? 0 : (a.group == 64 ? 1 : 2);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = (long long)p.n_tiles * p.m_tiles;
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = smem_bytes(nt);
+  B200Q_CUDA_OK(cudaFuncSetAttribute(qmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  qmm_tc_kernel<<<grid, kThreads, smem, st>>>(map_x, map_w, p);
+  B200Q_LAUNCH_OK("qmm_tc_kernel");
+  return B200Q_OK;
+}
+
 }  // namespace b200q

