@@ -300,7 +300,19 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     const int row_groups = p.K >> (5 + p.group_shift);
     uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+    // The arrival for an A stage is deferred until the next stage has been unpacked, so the
+    // latency of the tensor-memory store overlaps the next block's ALU work.
+    bool pending = false;
+    uint32_t pending_sa = 0;
+    auto publish = [&]() {
+      tcgen05_wait_st();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[pending_sa]));
+      pending = false;
+    };
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles && !*abort_flag; tile += gridDim.x) {
       const int tn = tile / p.m_tiles;
       int row = tn * kTileN + row_in_tile;
       row = row < p.N ? row : p.N - 1;  // rows past N: packed data is zero-filled by TMA
@@ -308,7 +320,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       const unsigned short* bi = reinterpret_cast<const unsigned short*>(p.biases) + (size_t)row * row_groups;
       uint32_t s_next = __ldg(sc + ((half * 32) >> (5 + p.group_shift)));
       uint32_t b_next = __ldg(bi + ((half * 32) >> (5 + p.group_shift)));
-      bool ok = true;
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
         const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
@@ -324,16 +335,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
         uint32_t vals[16];
         dequant32_b4(w, s_cur * 0x00010001u, b_cur * 0x00010001u, vals);
+        if (pending) publish();
         if (!mbar_wait(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         tcgen05_st_x16(tmem_a + lane_field + sa * 32 + half * 16, vals);
-        tcgen05_wait_st();
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[sa]));
+        pending = true;
+        pending_sa = sa;
       }
-      if (!ok) break;
     }
+    if (pending) publish();
   } else {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;
