@@ -140,6 +140,26 @@ int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* wq, const vo
                    void* stream);
 
 /*
+ * Decode (1 <= M <= 16 rows of bfloat16 x, transpose form) for callers that cannot
+ * allocate device memory and therefore cannot supply the workspace b200q_qmm needs:
+ * e.g. a plugin running under a host framework's allocator or capture rules, or a
+ * serving loop that bans allocator calls after start-up.  This entry point has no
+ * counterpart in the reference project.  It allocates nothing: its scratch is a fixed
+ * array inside the library image (about 2 MiB of device memory on every GPU that loads
+ * the library, held until the process exits), large enough for
+ * N <= B200Q_STATIC_SCRATCH_MAX_N weight rows; a larger N is rejected with
+ * B200Q_ERR_UNSUPPORTED.  The first call on each device looks up the array's device
+ * address; make that first call outside any stream capture.  All calls on a device
+ * share the array: calls that may overlap on the GPU race on it and must be
+ * serialised by the caller.  The used part is cleared on `stream` before every launch.
+ * Same results as b200q_qmm on the same inputs.
+ */
+#define B200Q_STATIC_SCRATCH_MAX_N 32768
+int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                            void* y, int dtype, int64_t M, int64_t N, int64_t K, int group_size,
+                            int bits, void* stream);
+
+/*
  * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
  * launch for this problem ("qmv_bulk", "qmv_mma", "qmm_tcgen05", "qmm_generic").
  */

@@ -495,4 +495,77 @@ int qmv_mma(const QmmArgs& a, cudaStream_t st) {
   return rc;
 }
 
+// ------------------------------------------------------------------------------------
+// Decode without any allocation by anyone: the scratch of the kernel above lives in a
+// fixed device array that is part of the loaded library image.
+//
+// Who needs this: code that may not call cudaMalloc at the point where it runs the
+// operator - a plugin invoked inside someone else's memory-pool or capture discipline, a
+// real-time serving loop that forbids allocator calls after start-up, a host that only
+// hands out buffers for inputs and outputs.  Such a caller cannot provide the workspace
+// b200q_qmm asks for, so this entry point brings its own.
+//
+// Cost and limits: every GPU that loads the library holds kStaticScratchBytes (about 2 MiB)
+// until the process exits.  The array is sized for N <= B200Q_STATIC_SCRATCH_MAX_N weight
+// rows; larger problems are rejected.  All calls on a device share the one array, so two
+// calls that can overlap on the GPU (different streams, or graph branches) race on it:
+// serialise them.  The array keeps whatever the previous call left; the part a call uses
+// is cleared on the stream before the kernel runs.
+constexpr size_t kStaticScratchBytes =
+    ((B200Q_STATIC_SCRATCH_MAX_N + 15) / 16 * 4 + 255) / 256 * 256 +           // arrival counters
+    (size_t)((B200Q_STATIC_SCRATCH_MAX_N + 31) / 32 * 32) * 16 * 4 + 256;      // fp32 partial tiles + status
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_static_scratch per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use: the address has to be asked for,
+// once per device, with that device current.
+int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  B200Q_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200Q_ERR_UNSUPPORTED, "[decode_static] device ordinal %d not supported", dev);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    B200Q_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return B200Q_OK;
+}
+}  // namespace
+
 }  // namespace b200q
+
+extern "C" int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                                       void* y, int dtype, int64_t M, int64_t N, int64_t K, int group_size,
+                                       int bits, void* stream) {
+  using namespace b200q;
+  if (dtype != B200Q_BF16)
+    return fail(B200Q_ERR_UNSUPPORTED, "[decode_static] only bfloat16 is supported (dtype code %d)", dtype);
+  if (!valid_group(group_size) || !valid_bits(bits))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[decode_static] unsupported group_size %d / bits %d", group_size, bits);
+  if (M < 1 || M > 16 || N < 1 || K < 128 || K % 128 != 0 || K % group_size != 0)
+    return fail(B200Q_ERR_UNSUPPORTED,
+                "[decode_static] needs 1 <= M <= 16 and K a multiple of 128 (got M=%lld N=%lld K=%lld)",
+                (long long)M, (long long)N, (long long)K);
+  if (N > B200Q_STATIC_SCRATCH_MAX_N)
+    return fail(B200Q_ERR_UNSUPPORTED,
+                "[decode_static] N=%lld exceeds the built-in scratch (at most %d weight rows); "
+                "use b200q_qmm with a caller workspace", (long long)N, (int)B200Q_STATIC_SCRATCH_MAX_N);
+  if (!x || !wq || !scales || !biases || !y) return fail(B200Q_ERR_INVALID_ARGUMENT, "[decode_static] null pointer");
+  QmmArgs a{};
+  a.x = x; a.wq = wq; a.scales = scales; a.biases = biases; a.y = y;
+  a.dtype = dtype; a.batch = 1; a.M = M; a.N = N; a.K = K;
+  a.group = group_size; a.bits = bits; a.transpose = true; a.w_batched = false;
+  if (!qmv_mma_supported(a))
+    return fail(B200Q_ERR_UNSUPPORTED, "[decode_static] x and wq must be 16-byte aligned and x must fit in shared memory");
+  void* scratch = nullptr;
+  if (int rc = static_scratch_ptr(&scratch)) return rc;  // first call on a device: set-up (not capturable)
+  const size_t used = qmv_mma_workspace_bytes(a);  // <= kStaticScratchBytes by the N check above
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200Q_CUDA_OK(cudaMemsetAsync(scratch, 0, used, st));  // counters and partial sums must start at zero
+  a.ws = scratch;
+  a.ws_bytes = used;
+  return qmv_mma(a, st);
+}
