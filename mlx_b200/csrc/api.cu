@@ -32,7 +32,7 @@ void count_launch(int n) { g_launches += (uint64_t)n; }
 
 namespace {
 
-enum class Path { QmvBulk, Qmv, Tc, Generic };
+enum class Path { QmvTc, QmvBulk, Qmv, Tc, Generic };
 
 int check_qmm_args(const char* tag, const QmmArgs& a) {
   if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
@@ -59,7 +59,7 @@ int qmv_override() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_QMV_IMPL");
-    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : 0));
+    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : 0)));
   }
   return v;
 }
@@ -77,6 +77,7 @@ Path choose(const QmmArgs& a) {
   const int ov = qmv_override();
   if (force_tc() && qmm_tc_supported(a)) return Path::Tc;  // tuning aid: tensor-memory path for any M
   // The register-path kernel is currently the faster of the two decode kernels.
+  if (ov == 3 && qmv_tc_supported(a)) return Path::QmvTc;
   if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
   if (qmv_mma_supported(a)) return Path::Qmv;
   if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
@@ -109,6 +110,7 @@ int run_qmm(const QmmArgs& a, cudaStream_t st) {
   if (!a.x || !a.wq || !a.scales || !a.biases || !a.y)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null pointer");
   switch (choose(a)) {
+    case Path::QmvTc: return qmv_tc(a, st);
     case Path::QmvBulk: return qmv_bulk(a, st);
     case Path::Qmv: return qmv_mma(a, st);
     case Path::Tc: return qmm_tc(a, st);
@@ -135,6 +137,8 @@ extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M,
   size_t q = qmv_mma_workspace_bytes(a);
   const size_t qb = qmv_bulk_workspace_bytes(a);
   q = q > qb ? q : qb;
+  const size_t qt = qmv_tc_workspace_bytes(a);
+  q = q > qt ? q : qt;
   size_t t = qmm_tc_workspace_bytes(a);
   need = q > t ? q : t;
   return (need + 255) / 256 * 256;
@@ -156,6 +160,7 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
                         group_size, bits, transpose, 0, nullptr, 0);
   if (check_qmm_args("quantized_matmul", a)) return "invalid";
   switch (choose(a)) {
+    case Path::QmvTc: return "qmv_tc";
     case Path::QmvBulk: return "qmv_bulk";
     case Path::Qmv: return "qmv_mma";
     case Path::Tc: return "qmm_tcgen05";

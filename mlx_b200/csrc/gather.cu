@@ -1,16 +1,147 @@
 // gather_qmm: out[i] = x[lhs[i]] * dequant(w[rhs[i]])  (GatherQMM::eval_gpu,
 // mlx/backend/cuda/quantized/quantized.cpp:154-278; CPU semantics
 // mlx/backend/cpu/quantized.cpp:700-747).
+//
+// Fast path (bf16, transpose, 4-bit): the index pairs are sorted by weight matrix (expert)
+// with a counting sort on the device, the activation rows are gathered into expert order,
+// and ONE grouped launch of the tensor-core kernel (qmm_tcgen05.cu) runs a tile list of
+// (expert, up to NT rows, 128 weight rows); its epilogue scatters every row back to the
+// position of its index pair.  Each expert's weights are read once per NT rows instead of
+// once per index pair (the reference launches one independent M x N x K problem per pair).
+// Everything else goes through the shape-agnostic kernel with per-problem index lookups.
+//
+// Scratch (caller workspace): [header | sorted slots | destination rows | tile table |
+// gathered activations | status].  No host synchronisation: tile counts stay on the device.
+#include <cmath>
+
 #include "common.cuh"
 #include "kernels.h"
+
+namespace b200q {
+namespace {
+
+struct MTileRec { int expert, row0, rows, pad; };  // layout of MTile in qmm_tcgen05.cu
+
+struct Header { int n_mtiles; int n_rows_valid; int pad[62]; };
+
+constexpr int kMaxExpertsFast = 1024;
+
+__global__ void __launch_bounds__(1024)
+gather_sort_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs, int n_idx, uint32_t x_batch,
+                   uint32_t E, int M, int NT, Header* hdr, int* __restrict__ sorted_slot, MTileRec* __restrict__ mtiles,
+                   void* y, size_t y_slot_bytes, uint32_t* status) {
+  __shared__ int counts[kMaxExpertsFast];
+  __shared__ int cursor[kMaxExpertsFast];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < (int)E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < n_idx; i += blockDim.x) {
+    const uint32_t e = rhs[i], l = lhs[i];
+    if (e < E && l < x_batch) {
+      atomicAdd(&counts[e], 1);
+    } else {
+      // out-of-range index: record it; its output rows are zeroed below, nothing is read through it
+      atomicMax(&status[0], 1u);
+      status[1] = (uint32_t)i;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int slot0 = 0, g = 0;
+    for (int e = 0; e < (int)E; ++e) {
+      cursor[e] = slot0;
+      const int rows = counts[e] * M, row0 = slot0 * M;
+      for (int r = 0; r < rows; r += NT) {
+        mtiles[g].expert = e;
+        mtiles[g].row0 = row0 + r;
+        mtiles[g].rows = rows - r < NT ? rows - r : NT;
+        mtiles[g].pad = 0;
+        ++g;
+      }
+      slot0 += counts[e];
+    }
+    hdr->n_mtiles = g;
+    hdr->n_rows_valid = slot0 * M;
+  }
+  __syncthreads();
+  for (int i = tid; i < n_idx; i += blockDim.x) {
+    const uint32_t e = rhs[i], l = lhs[i];
+    if (e < E && l < x_batch) {
+      sorted_slot[atomicAdd(&cursor[e], 1)] = i;
+    } else {
+      unsigned short* dst = reinterpret_cast<unsigned short*>(static_cast<char*>(y) + (size_t)i * y_slot_bytes);
+      for (size_t b = 0; b < y_slot_bytes / 2; ++b) dst[b] = 0;
+    }
+  }
+}
+
+// One CTA per activation row of the sorted order: copies x[lhs[slot]] row m and records where
+// the result row goes.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ lhs, const Header* hdr,
+                   const int* __restrict__ sorted_slot, int M, int K, __nv_bfloat16* __restrict__ x_sorted,
+                   int* __restrict__ dst_row) {
+  const int r = blockIdx.x;
+  if (r >= hdr->n_rows_valid) return;
+  const int slot = sorted_slot[r / M], m = r % M;
+  const uint4* src = reinterpret_cast<const uint4*>(x + ((size_t)lhs[slot] * M + m) * K);
+  uint4* dst = reinterpret_cast<uint4*>(x_sorted + (size_t)r * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = __ldg(src + i);
+  if (threadIdx.x == 0) dst_row[r] = slot * M + m;
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Rows per tile: the mean rows per expert plus three standard deviations of a uniform
+// routing (so that most experts fit one tile without padding it to 256 tokens).
+int pick_nt(int64_t n_rows, int64_t E) {
+  const double avg = (double)n_rows / (double)(E > 0 ? E : 1);
+  int64_t nt = (int64_t)(avg + 3.0 * sqrt(avg) + 8.0);
+  nt = (nt + 15) / 16 * 16;
+  return (int)(nt < 16 ? 16 : (nt > 256 ? 256 : nt));
+}
+
+struct FastLayout {
+  size_t hdr, sorted, dst, mtiles, xs, total;
+  int64_t n_rows, max_mtiles;
+  int nt;
+};
+
+FastLayout fast_layout(int64_t n_idx, int64_t E, int64_t M, int64_t K) {
+  FastLayout L{};
+  L.n_rows = n_idx * M;
+  L.nt = pick_nt(L.n_rows, E);
+  L.max_mtiles = L.n_rows / L.nt + E + 1;
+  size_t off = 0;
+  L.hdr = off; off += align256(sizeof(Header));
+  L.sorted = off; off += align256((size_t)n_idx * 4);
+  L.dst = off; off += align256((size_t)L.n_rows * 4);
+  L.mtiles = off; off += align256((size_t)L.max_mtiles * sizeof(MTileRec));
+  L.xs = off; off += align256((size_t)L.n_rows * K * 2);
+  L.total = off + 256;  // status word lives in the last 16 bytes
+  return L;
+}
+
+bool fast_supported(int dtype, int64_t n_idx, int64_t x_batch, int64_t E, int64_t M, int64_t N, int64_t K, int group,
+                    int bits, int transpose) {
+  (void)x_batch; (void)group;
+  if (dtype != B200Q_BF16 || !transpose || bits != 4) return false;
+  if (E < 1 || E > kMaxExpertsFast || n_idx < 1 || M < 1 || N < 1) return false;
+  if (K < 64 || K % 64 != 0) return false;
+  if (n_idx * M > (1ll << 30) || E * N > (1ll << 31) - 1) return false;
+  return true;
+}
+
+}  // namespace
+}  // namespace b200q
 
 using namespace b200q;
 
 extern "C" size_t b200q_gather_qmm_workspace_bytes(int dtype, int64_t n_idx, int64_t x_batch, int64_t E,
                                                    int64_t M, int64_t N, int64_t K, int group_size, int bits,
                                                    int transpose) {
-  (void)dtype; (void)n_idx; (void)x_batch; (void)E; (void)M; (void)N; (void)K;
-  (void)group_size; (void)bits; (void)transpose;
+  if (fast_supported(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose))
+    return fast_layout(n_idx, E, M, K).total;
   return 256;  // status word only
 }
 
@@ -43,16 +174,40 @@ extern "C" int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* s
   }
   if (!x || !wq || !scales || !biases || !lhs_idx || !rhs_idx || !y)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm] null pointer");
-  if (!ws || ws_bytes < kStatusBytes)
-    return fail(B200Q_ERR_WORKSPACE, "[gather_qmm] workspace of %zu bytes required, %zu given",
-                b200q_gather_qmm_workspace_bytes(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose), ws_bytes);
+  const size_t need = b200q_gather_qmm_workspace_bytes(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose);
+  if (!ws || ws_bytes < need)
+    return fail(B200Q_ERR_WORKSPACE, "[gather_qmm] workspace of %zu bytes required, %zu given", need, ws_bytes);
+  uint32_t* status = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes);
+
+  const bool aligned = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wq) |
+                          reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(y)) & 15);
+  if (aligned && fast_supported(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose)) {
+    const FastLayout L = fast_layout(n_idx, E, M, K);
+    char* base = static_cast<char*>(ws);
+    Header* hdr = reinterpret_cast<Header*>(base + L.hdr);
+    int* sorted = reinterpret_cast<int*>(base + L.sorted);
+    int* dst = reinterpret_cast<int*>(base + L.dst);
+    MTileRec* mt = reinterpret_cast<MTileRec*>(base + L.mtiles);
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + L.xs);
+    gather_sort_kernel<<<1, 1024, 0, st>>>(lhs_idx, rhs_idx, (int)n_idx, (uint32_t)x_batch, (uint32_t)E, (int)M, L.nt,
+                                           hdr, sorted, mt, y, (size_t)M * N * 2, status);
+    B200Q_LAUNCH_OK("gather_sort_kernel");
+    gather_rows_kernel<<<(unsigned)L.n_rows, 256, 0, st>>>((const __nv_bfloat16*)x, lhs_idx, hdr, sorted, (int)M, (int)K,
+                                                           xs, dst);
+    B200Q_LAUNCH_OK("gather_rows_kernel");
+    GroupedArgs g{};
+    g.x_sorted = xs; g.wq = wq; g.scales = scales; g.biases = biases; g.y = y;
+    g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles; g.dst_row = dst;
+    g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E; g.N = N; g.K = K;
+    g.group = group_size; g.nt = L.nt; g.status = status;
+    return qmm_tc_grouped(g, st);
+  }
 
   QmmArgs a{};
   a.x = x; a.wq = wq; a.scales = scales; a.biases = biases; a.y = y;
   a.dtype = dtype; a.batch = n_idx; a.M = M; a.N = N; a.K = K;
   a.group = group_size; a.bits = bits; a.transpose = transpose != 0; a.w_batched = true;
   a.ws = ws; a.ws_bytes = ws_bytes;
-  GatherIdx gi{lhs_idx, rhs_idx, (uint32_t)x_batch, (uint32_t)E,
-               reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes)};
+  GatherIdx gi{lhs_idx, rhs_idx, (uint32_t)x_batch, (uint32_t)E, status};
   return qmm_generic(a, st, &gi);
 }

@@ -24,21 +24,20 @@ struct QmmArgs {
   size_t ws_bytes;
 };
 
-// Grouped (mixture-of-experts) problem: rows of x sorted by expert, one segment per
-// expert.  All arrays live on the device and are produced by the sort kernels.
+// Grouped (mixture-of-experts) problem for the tensor-core kernel: activation rows sorted by
+// expert; the tile table lives on the device and is produced by the sort kernel of gather.cu.
 struct GroupedArgs {
-  const void* x_sorted;        // [n_rows, K] activations gathered in expert order
-  const uint32_t* wq;          // [E, N, K*bits/32]
-  const void* scales;          // [E, N, K/g]
+  const void* x_sorted;     // [n_rows, K] bf16, rows in expert order
+  const uint32_t* wq;       // [E, N, K/8] packed 4-bit
+  const void* scales;       // [E, N, K/g]
   const void* biases;
-  void* y;                     // [n_rows_out, N]; row of sorted position p is dst_row[p]
-  const int32_t* seg_start;    // [E+1] first sorted row of each expert
-  const int32_t* dst_row;      // [n_rows] destination row in y of each sorted row
-  int dtype;
-  int64_t n_rows, E, N, K;
-  int group, bits;
-  void* ws;
-  size_t ws_bytes;
+  void* y;                  // [n_rows, N]; activation row p is written to row dst_row[p]
+  const void* mtiles;       // device: MTile[max_mtiles]
+  const int* n_mtiles;      // device scalar
+  const int* dst_row;       // device: [n_rows]
+  int64_t n_rows, max_mtiles, E, N, K;
+  int group, nt;
+  uint32_t* status;
 };
 
 // Per-problem operand selection of the gather form: problem i of `batch` multiplies
@@ -64,9 +63,15 @@ bool qmv_bulk_supported(const QmmArgs& a);
 size_t qmv_bulk_workspace_bytes(const QmmArgs& a);
 int qmv_bulk(const QmmArgs& a, cudaStream_t st);
 
+// qmv_tc.cu : decode path on tcgen05 (thread-per-row unpack into TMEM, per-group accumulators)
+bool qmv_tc_supported(const QmmArgs& a);
+size_t qmv_tc_workspace_bytes(const QmmArgs& a);
+int qmv_tc(const QmmArgs& a, cudaStream_t st);
+
 // qmm_tcgen05.cu : prefill path (TMA + tcgen05 + TMEM), transpose only, bf16
 bool qmm_tc_supported(const QmmArgs& a);
 size_t qmm_tc_workspace_bytes(const QmmArgs& a);
 int qmm_tc(const QmmArgs& a, cudaStream_t st);
+int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st);
 
 }  // namespace b200q

@@ -27,6 +27,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_ptx.cuh"
 
 namespace b200q {
 namespace {
@@ -41,113 +42,8 @@ constexpr int kTmemCols = 512;
 constexpr int kDequantWarps = 8;
 constexpr int kEpilogueWarps = 4;
 constexpr int kThreads = 32 * (2 + kDequantWarps + kEpilogueWarps);  // 448
-constexpr uint32_t kSpinLimit = 1u << 21;
 
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait; also gives up as soon as another role has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try(bar, parity)) return true;
-    if (i > 8) {
-      __nanosleep(32);
-      if ((i & 63) == 0 && *abort_flag) return false;
-    }
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tcgen05_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem descriptor]
-__device__ __forceinline__ void tcgen05_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
+using namespace tc;
 
 // Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand tile whose
 // rows are 128 bytes (64 bf16): 8-row groups are 1024 bytes apart (SBO), descriptor
@@ -167,7 +63,19 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
 }
 
+// One entry per group of NT consecutive rows of the (expert-sorted) activation matrix.
+struct MTile {
+  int expert;     // weight matrix the rows multiply
+  int row0;       // first row in the activation matrix
+  int rows;       // valid rows (<= NT): the rest of the TMA box belongs to another expert
+  int pad;
+};
+
 struct TcParams {
+  // grouped (gather_qmm) mode: device-side tile table, else nullptr
+  const MTile* mtiles;
+  const int* n_mtiles;      // device scalar: entries of `mtiles`
+  const int* dst_row;       // output row of every activation row
   const __nv_bfloat16* scales;
   const __nv_bfloat16* biases;
   __nv_bfloat16* y;
@@ -208,6 +116,34 @@ __device__ __forceinline__ void dequant32_b4(const uint4 w, uint32_t s2, uint32_
   }
 }
 
+struct TileCoord {
+  int w_row0;   // first row of the tile in the stacked weight tensor [E*N, ...]
+  int w_rows_end;  // one past the last valid stacked row of this expert
+  int n0;       // first output column
+  int x_row0;   // first activation row
+  int rows;     // valid activation rows
+};
+__device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile) {
+  TileCoord t;
+  if (p.mtiles == nullptr) {
+    const int tm = tile % p.m_tiles, tn = tile / p.m_tiles;
+    t.w_row0 = tn * kTileN;
+    t.w_rows_end = p.N;
+    t.n0 = tn * kTileN;
+    t.x_row0 = tm * p.NT;
+    t.rows = p.M - t.x_row0 < p.NT ? p.M - t.x_row0 : p.NT;
+  } else {
+    const int g = tile / p.n_tiles, tn = tile - g * p.n_tiles;
+    const MTile mt = p.mtiles[g];
+    t.w_row0 = mt.expert * p.N + tn * kTileN;
+    t.w_rows_end = mt.expert * p.N + p.N;
+    t.n0 = tn * kTileN;
+    t.x_row0 = mt.row0;
+    t.rows = mt.rows;
+  }
+  return t;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const TcParams p) {
@@ -223,7 +159,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = p.K / kBlockK;
-  const int total_tiles = p.n_tiles * p.m_tiles;
+  const int total_tiles = p.mtiles ? *p.n_mtiles * p.n_tiles : p.n_tiles * p.m_tiles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStagesP; ++i) { mbar_init(smem_u32(&bars->full_p[i]), 1); mbar_init(smem_u32(&bars->empty_p[i]), kDequantWarps); }
@@ -250,16 +186,16 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0;  // k-block counter across tiles
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const int tm = tile % p.m_tiles, tn = tile / p.m_tiles;
+        const TileCoord tc_ = tile_coord(p, tile);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
           const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
           if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) break;
           mbar_expect_tx(smem_u32(&bars->full_p[sp]), kTileN * 32);
-          tma_load_2d(smem_u32(ring_p + sp * (kTileN * 32)), &map_w, kb * 32, tn * kTileN, smem_u32(&bars->full_p[sp]));
+          tma_load_2d(smem_u32(ring_p + sp * (kTileN * 32)), &map_w, kb * 32, tc_.w_row0, smem_u32(&bars->full_p[sp]));
           if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) break;
           mbar_expect_tx(smem_u32(&bars->full_b[sb]), b_stage_bytes);
-          tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tm * p.NT, smem_u32(&bars->full_b[sb]));
+          tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tc_.x_row0, smem_u32(&bars->full_b[sb]));
         }
       }
     }
@@ -313,9 +249,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     };
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-      const int tn = tile / p.m_tiles;
-      int row = tn * kTileN + row_in_tile;
-      row = row < p.N ? row : p.N - 1;  // rows past N: packed data is zero-filled by TMA
+      const TileCoord tc_ = tile_coord(p, tile);
+      int row = tc_.w_row0 + row_in_tile;
+      row = row < tc_.w_rows_end ? row : tc_.w_rows_end - 1;  // rows past N: results are never stored
       const unsigned short* sc = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * row_groups;
       const unsigned short* bi = reinterpret_cast<const unsigned short*>(p.biases) + (size_t)row * row_groups;
       uint32_t s_next = __ldg(sc + ((half * 32) >> (5 + p.group_shift)));
@@ -350,11 +286,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const int tm = tile % p.m_tiles, tn = tile / p.m_tiles;
+      const TileCoord tc_ = tile_coord(p, tile);
       if (!mbar_wait(smem_u32(&bars->acc_full), tcount & 1, abort_flag)) break;
       tcgen05_fence_after();
-      const int n = tn * kTileN + quad * 32 + lane;
-      const int m0 = tm * p.NT;
+      const int n = tc_.n0 + quad * 32 + lane;
+      const int m0 = tc_.x_row0;
       for (int c = 0; c < p.NT; c += 32) {
         uint32_t v[32];
         tcgen05_ld_x32(tmem_acc + lane_field + c, v);
@@ -362,8 +298,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if (n < p.N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int m = m0 + c + j;
-            if (c + j < p.NT && m < p.M) p.y[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            if (c + j < tc_.rows) {
+              const int m = p.dst_row ? p.dst_row[m0 + c + j] : m0 + c + j;
+              p.y[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
           }
         }
       }
@@ -479,5 +417,57 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
   B200Q_LAUNCH_OK("qmm_tc_kernel");
   return B200Q_OK;
 }
+
+int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(B200Q_ERR_CUDA, "[gather_qmm] cuTensorMapEncodeTiled is not available");
+  const int nt = a.nt;
+  CUtensorMap map_x, map_w;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.n_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)nt};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x_sorted), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[gather_qmm] tensor map for x failed (%d)", (int)r);
+  }
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K / 2, (cuuint64_t)(a.E * a.N)};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K / 2};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.wq), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[gather_qmm] tensor map for w failed (%d)", (int)r);
+  }
+  TcParams p{};
+  p.mtiles = static_cast<const MTile*>(a.mtiles);
+  p.n_mtiles = a.n_mtiles;
+  p.dst_row = a.dst_row;
+  p.scales = (const __nv_bfloat16*)a.scales;
+  p.biases = (const __nv_bfloat16*)a.biases;
+  p.y = (__nv_bfloat16*)a.y;
+  p.status = a.status;
+  p.M = (int)a.n_rows; p.N = (int)a.N; p.K = (int)a.K;
+  p.NT = nt;
+  p.n_tiles = (int)((a.N + kTileN - 1) / kTileN);
+  p.m_tiles = 0;
+  p.group_shift = a.group == 32 ? 0 : (a.group == 64 ? 1 : 2);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = (long long)p.n_tiles * a.max_mtiles;  // upper bound; the kernel reads the exact count
+  const int grid = (int)(tiles < sms ? tiles : sms);
+  const size_t smem = smem_bytes(nt);
+  B200Q_CUDA_OK(cudaFuncSetAttribute(qmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  qmm_tc_kernel<<<grid, kThreads, smem, st>>>(map_x, map_w, p);
+  B200Q_LAUNCH_OK("qmm_tc_kernel");
+  return B200Q_OK;
+}
+
+size_t qmm_tc_mtile_bytes() { return sizeof(MTile); }
 
 }  // namespace b200q

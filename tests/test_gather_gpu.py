@@ -71,3 +71,75 @@ def test_gather_bad_index_is_flagged_not_faulted():
     rc = _lib.load().b200q_read_status(ctypes.c_void_p(ws.data_ptr()), ws.numel(),
                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), st)
     assert rc == 0 and st[0] == 1 and st[1] == 1
+
+
+# ---- sort-by-expert grouped path (bf16, 4-bit, transpose) -------------------------------
+def _moe_case(E, tokens, topk, N, K, M=1, g=64, seed=0):
+    dtype = "bf16"
+    wq, s, b = O.quantize(make_w(100 + seed, (E, N, K), dtype), g, 4, dtype)
+    x = make_x(1 + seed, (tokens, M, K), dtype)
+    rng = np.random.default_rng(3 + seed)
+    rhs = rng.permuted(np.tile(np.arange(E), (tokens, 1)), axis=1)[:, :topk].astype(np.uint32)
+    lhs = np.broadcast_to(np.arange(tokens, dtype=np.uint32)[:, None], rhs.shape).copy()
+    return dtype, wq, s, b, x, lhs, rhs
+
+
+@pytest.mark.parametrize("E,tokens,topk,N,K,M,g", [(8, 64, 2, 256, 512, 1, 64), (4, 33, 2, 200, 256, 1, 32),
+                                                    (8, 512, 2, 1024, 4096, 1, 64), (3, 10, 1, 128, 128, 3, 128),
+                                                    (16, 7, 4, 384, 1024, 2, 64)])
+def test_gather_grouped_vs_oracle(E, tokens, topk, N, K, M, g):
+    dtype, wq, s, b, x, lhs, rhs = _moe_case(E, tokens, topk, N, K, M, g)
+    y = mb.gather_qmm(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype),
+                      lhs_indices=torch.from_numpy(lhs.astype(np.int64)), rhs_indices=torch.from_numpy(rhs.astype(np.int64)),
+                      group_size=g, bits=4)
+    assert tuple(y.shape) == (tokens, topk, M, N)
+    ref = O.gather_qmm(O.to_f32(x, dtype), wq, O.to_f32(s, dtype), O.to_f32(b, dtype), lhs.ravel(), rhs.ravel(), True,
+                       g, 4, "f32")
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype).reshape(ref.shape), ref)
+    assert ok, rel
+
+
+def test_gather_grouped_full_size_moe_layer():
+    """Mixtral-style layer: 8 experts [14336, 4096], 512 tokens, top-2.  Every output slot must equal
+    the plain quantized_matmul of its token with its expert (the kernels share no code path for the
+    gather), and sampled slots are checked against the oracle."""
+    E, tokens, topk, N, K = 8, 512, 2, 14336, 4096
+    dtype, wq, s, b, x, lhs, rhs = _moe_case(E, tokens, topk, N, K)
+    wq_t, s_t, b_t = u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype)
+    x_t = to_torch(x, dtype)
+    y = mb.gather_qmm(x_t, wq_t, s_t, b_t, rhs_indices=torch.from_numpy(rhs.astype(np.int64)),
+                      lhs_indices=torch.from_numpy(lhs.astype(np.int64)))
+    assert tuple(y.shape) == (tokens, topk, 1, N)
+    rhs_t = torch.from_numpy(rhs.astype(np.int64)).cuda()
+    for e in range(E):
+        tok, slot = torch.nonzero(rhs_t == e, as_tuple=True)
+        ye = mb.quantized_matmul(x_t[tok, 0], wq_t.view(torch.int32)[e].view(torch.uint32), s_t[e], b_t[e])
+        got = y[tok, slot, 0]
+        assert torch.allclose(got.float(), ye.float(), rtol=2e-2, atol=2e-2), e
+    idx = [(0, 0), (17, 1), (511, 1), (300, 0)]
+    for t, k in idx:
+        e = int(rhs[t, k])
+        ref = O.qmm_f32_from(x[t], wq[e], s[e], b[e], dtype, transpose=True, group_size=64, bits=4)
+        ok, rel = qmm_close(O.to_f32(from_torch(y[t, k]), dtype), ref)
+        assert ok, rel
+
+
+def test_gather_grouped_bad_index_flagged():
+    from mlx_b200 import _lib, ops
+    import ctypes
+    dtype, wq, s, b, x, lhs, rhs = _moe_case(4, 16, 2, 128, 256)
+    rhs[5, 1] = 77  # out of range expert
+    y = mb.gather_qmm(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype),
+                      lhs_indices=torch.from_numpy(lhs.astype(np.int64)), rhs_indices=torch.from_numpy(rhs.astype(np.int64)))
+    torch.cuda.synchronize()
+    assert bool((y[5, 1] == 0).all()) and bool((y[5, 0] != 0).any())
+    ws = ops._workspaces.get(y.device, 0)
+    st = (ctypes.c_uint32 * 4)()
+    rc = _lib.load().b200q_read_status(ctypes.c_void_p(ws.data_ptr()), ws.numel(),
+                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), st)
+    assert rc == 0 and st[0] == 1 and st[1] == 5 * 2 + 1
+    good = np.ones(rhs.shape, bool); good[5, 1] = False
+    ref = O.gather_qmm(O.to_f32(x, dtype), wq, O.to_f32(s, dtype), O.to_f32(b, dtype), lhs[good], rhs[good], True, 64, 4, "f32")
+    got = O.to_f32(from_torch(y), dtype)[good]
+    ok, rel = qmm_close(got.reshape(ref.shape), ref)
+    assert ok, rel

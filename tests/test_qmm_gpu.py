@@ -140,9 +140,11 @@ def test_mixed_dtype_promotes_to_float32():
     assert ok, rel
 
 
-def test_qmv_bulk_variant_in_subprocess():
-    """The bulk-copy staged decode kernel is selected with B200Q_QMV_IMPL=bulk; run a few
-    shapes through it in a child process (the override is read once per process)."""
+@pytest.mark.parametrize("impl", ("bulk", "tc"))
+def test_qmv_alternative_kernels_in_subprocess(impl):
+    """The bulk-copy staged (mma.sync) and the tensor-memory (tcgen05) decode kernels are selected
+    with B200Q_QMV_IMPL=bulk|tc; run a few shapes through each in a child process (the override is
+    read once per process)."""
     import subprocess
     import sys
     code = r'''
@@ -151,7 +153,7 @@ sys.path.insert(0, "tests")
 import torch, oracle as O, mlx_b200 as mb
 from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch
 for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048, 32), (13, 4104, 4096, 128), (5, 520, 8192, 64)]:
-    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4) == "qmv_bulk"
+    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4) == "qmv_" + sys.argv[1]
     wq, s, b = O.quantize(make_w(N, (N, K), "bf16"), g, 4, "bf16")
     x = make_x(M, (M, K), "bf16")
     ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
@@ -161,9 +163,9 @@ for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048,
     assert ok, (M, N, K, g, rel)
 print("bulk-ok")
 '''
-    env = dict(os.environ, B200Q_QMV_IMPL="bulk")
+    env = dict(os.environ, B200Q_QMV_IMPL=impl)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    res = subprocess.run([sys.executable, "-c", code, impl], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "bulk-ok" in res.stdout, res.stdout + res.stderr
 
 
