@@ -2,7 +2,7 @@
 // mlx/backend/cuda/quantized/quantized.cpp:154-278; CPU semantics
 // mlx/backend/cpu/quantized.cpp:700-747).
 //
-// Fast path (bf16, transpose, 4-bit): the index pairs are sorted by weight matrix (expert)
+// Fast path (bf16, transpose, K a multiple of 128, every bit width): the index pairs are sorted by weight matrix (expert)
 // with a counting sort on the device, the activation rows are gathered into expert order,
 // and ONE grouped launch of the tensor-core kernel (qmm_tcgen05.cu) runs a tile list of
 // (expert, up to NT rows, 128 weight rows); its epilogue scatters every row back to the
@@ -125,9 +125,9 @@ FastLayout fast_layout(int64_t n_idx, int64_t E, int64_t M, int64_t K) {
 bool fast_supported(int dtype, int64_t n_idx, int64_t x_batch, int64_t E, int64_t M, int64_t N, int64_t K, int group,
                     int bits, int transpose) {
   (void)x_batch; (void)group;
-  if (dtype != B200Q_BF16 || !transpose || bits != 4) return false;
+  if (dtype != B200Q_BF16 || !transpose) return false;
   if (E < 1 || E > kMaxExpertsFast || n_idx < 1 || M < 1 || N < 1) return false;
-  if (K < 64 || K % 64 != 0) return false;
+  if (K < 128 || K % 128 != 0 || (K * bits / 8) % 16 != 0) return false;
   if (n_idx * M > (1ll << 30) || E * N > (1ll << 31) - 1) return false;
   return true;
 }
@@ -199,7 +199,7 @@ extern "C" int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* s
     g.x_sorted = xs; g.wq = wq; g.scales = scales; g.biases = biases; g.y = y;
     g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles; g.dst_row = dst;
     g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E; g.N = N; g.K = K;
-    g.group = group_size; g.nt = L.nt; g.status = status;
+    g.group = group_size; g.bits = bits; g.nt = L.nt; g.status = status;
     return qmm_tc_grouped(g, st);
   }
 

@@ -28,7 +28,7 @@ struct QmmArgs {
 // expert; the tile table lives on the device and is produced by the sort kernel of gather.cu.
 struct GroupedArgs {
   const void* x_sorted;     // [n_rows, K] bf16, rows in expert order
-  const uint32_t* wq;       // [E, N, K/8] packed 4-bit
+  const uint32_t* wq;       // [E, N, K*bits/32] packed
   const void* scales;       // [E, N, K/g]
   const void* biases;
   void* y;                  // [n_rows, N]; activation row p is written to row dst_row[p]
@@ -36,7 +36,7 @@ struct GroupedArgs {
   const int* n_mtiles;      // device scalar
   const int* dst_row;       // device: [n_rows]
   int64_t n_rows, max_mtiles, E, N, K;
-  int group, nt;
+  int group, bits, nt;
   uint32_t* status;
 };
 

@@ -40,8 +40,8 @@ constexpr int kStagesP = 4;       // packed W tiles in shared memory
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kDequantWarps = 8;
-constexpr int kEpilogueWarps = 4;
-constexpr int kThreads = 32 * (2 + kDequantWarps + kEpilogueWarps);  // 448
+constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each drains half of the columns
+constexpr int kThreads = 32 * (2 + kDequantWarps + kEpilogueWarps);  // 576
 
 using namespace tc;
 
@@ -95,24 +95,56 @@ struct __align__(8) Barriers {
   int abort_flag;
 };
 
-// Unpacks 32 consecutive 4-bit fields (4 words) of one row into 16 bf16x2 registers in
-// natural k order, applying w = s*q + b (one rounding).
-__device__ __forceinline__ void dequant32_b4(const uint4 w, uint32_t s2, uint32_t b2, uint32_t (&out)[16]) {
-  constexpr uint32_t kMagic = 0x43004300u;  // (128.0, 128.0): 0x4300 | q == 128 + q
-  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+// Unpacks 32 consecutive BITS-wide fields (BITS words, LSB-first bit stream) of one row into
+// 16 bf16x2 registers in natural k order, applying w = s*q + b (one rounding).  s and b are
+// the raw bf16 bit patterns.
+template <int BITS>
+__device__ __forceinline__ void dequant32(const uint32_t (&w)[BITS], uint32_t s_bits, uint32_t b_bits,
+                                          uint32_t (&out)[16]) {
+  constexpr uint32_t kMagic = 0x43004300u;  // (128.0, 128.0): 0x4300 | q == 128 + q for q < 128
+  const uint32_t s2 = s_bits * 0x00010001u, b2 = b_bits * 0x00010001u;
+  if constexpr (BITS == 4) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t p[4];
+    for (int j = 0; j < 4; ++j) {
+      uint32_t p[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      // p[i] = (q[i], q[i+4]) as bf16 pairs
-      const uint32_t t = lop3_and_or(ws[j] >> (4 * i), 0x000F000Fu, kMagic);
-      p[i] = fma_bf16x2(sub_bf16x2(t, kMagic), s2, b2);
+      for (int i = 0; i < 4; ++i) {
+        // p[i] = (q[i], q[i+4]) as bf16 pairs
+        const uint32_t t = lop3_and_or(w[j] >> (4 * i), 0x000F000Fu, kMagic);
+        p[i] = fma_bf16x2(sub_bf16x2(t, kMagic), s2, b2);
+      }
+      out[4 * j + 0] = __byte_perm(p[0], p[1], 0x5410);  // (w0, w1)
+      out[4 * j + 1] = __byte_perm(p[2], p[3], 0x5410);  // (w2, w3)
+      out[4 * j + 2] = __byte_perm(p[0], p[1], 0x7632);  // (w4, w5)
+      out[4 * j + 3] = __byte_perm(p[2], p[3], 0x7632);  // (w6, w7)
     }
-    out[4 * j + 0] = __byte_perm(p[0], p[1], 0x5410);  // (w0, w1)
-    out[4 * j + 1] = __byte_perm(p[2], p[3], 0x5410);  // (w2, w3)
-    out[4 * j + 2] = __byte_perm(p[0], p[1], 0x7632);  // (w4, w5)
-    out[4 * j + 3] = __byte_perm(p[2], p[3], 0x7632);  // (w6, w7)
+  } else if constexpr (BITS == 8) {
+    // 8-bit values exceed the bf16 integer trick: go through float (0x4B0000qq == 2^23 + q)
+    const float sf = __uint_as_float(s_bits << 16), bf = __uint_as_float(b_bits << 16);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t word = w[j >> 1];
+      const int b0 = (j & 1) * 2;
+      const float q0 = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540 | b0)) - 8388608.0f;
+      const float q1 = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7540 | (b0 + 1))) - 8388608.0f;
+      uint32_t d;
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(fmaf(q1, sf, bf)), "f"(fmaf(q0, sf, bf)));
+      out[j] = d;
+    }
+  } else {
+    constexpr uint32_t mask = (1u << BITS) - 1u;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t f[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = 2 * j + h, wi = (e * BITS) >> 5, sh = (e * BITS) & 31;
+        f[h] = (sh + BITS > 32) ? __funnelshift_r(w[wi], w[(wi + 1) % BITS], sh) : (w[wi] >> sh);
+      }
+      const uint32_t lo = lop3_and_or(f[0], mask, 0x4300u), hi = lop3_and_or(f[1], mask, 0x4300u);
+      const uint32_t t = __byte_perm(lo, hi, 0x5410);
+      out[j] = fma_bf16x2(sub_bf16x2(t, kMagic), s2, b2);
+    }
   }
 }
 
@@ -144,9 +176,14 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile) {
   return t;
 }
 
+template <int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const TcParams p) {
+  // A packed stage holds 128 k of every row (16*BITS bytes, a multiple of 16 for every width)
+  // and feeds two 64-k MMA blocks.
+  constexpr int kPRowBytes = 16 * BITS;
+  constexpr int kPStageBytes = kTileN * kPRowBytes;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // carve-up: [B ring: kStagesB * NT*128 B (1024-aligned)] [P ring: kStagesP * 4096 B] [barriers]
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -154,7 +191,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   const uint32_t b_stage_pitch = (b_stage_bytes + 1023u) & ~1023u;
   unsigned char* ring_b = smem;
   unsigned char* ring_p = ring_b + (size_t)kStagesB * b_stage_pitch;
-  Barriers* bars = reinterpret_cast<Barriers*>(ring_p + (size_t)kStagesP * (kTileN * 32));
+  Barriers* bars = reinterpret_cast<Barriers*>(ring_p + (size_t)kStagesP * kPStageBytes);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -188,11 +225,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc_ = tile_coord(p, tile);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
+          const uint32_t itp = it >> 1;  // packed stages advance every second k-block (kblocks is even)
+          const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
           const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
-          if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) break;
-          mbar_expect_tx(smem_u32(&bars->full_p[sp]), kTileN * 32);
-          tma_load_2d(smem_u32(ring_p + sp * (kTileN * 32)), &map_w, kb * 32, tc_.w_row0, smem_u32(&bars->full_p[sp]));
+          if ((it & 1) == 0) {
+            if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) break;
+            mbar_expect_tx(smem_u32(&bars->full_p[sp]), kPStageBytes);
+            tma_load_2d(smem_u32(ring_p + sp * kPStageBytes), &map_w, (kb >> 1) * kPRowBytes, tc_.w_row0,
+                        smem_u32(&bars->full_p[sp]));
+          }
           if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) break;
           mbar_expect_tx(smem_u32(&bars->full_b[sb]), b_stage_bytes);
           tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tc_.x_row0, smem_u32(&bars->full_b[sb]));
@@ -257,7 +298,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       uint32_t s_next = __ldg(sc + ((half * 32) >> (5 + p.group_shift)));
       uint32_t b_next = __ldg(bi + ((half * 32) >> (5 + p.group_shift)));
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1;
+        const uint32_t itp = it >> 1;
+        const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
         const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
         const uint32_t s_cur = s_next, b_cur = b_next;
         if (kb + 1 < kblocks) {
@@ -265,12 +307,35 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           s_next = __ldg(sc + g);
           b_next = __ldg(bi + g);
         }
-        if (!mbar_wait(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
-        const uint4 w = *reinterpret_cast<const uint4*>(ring_p + sp * (kTileN * 32) + row_in_tile * 32 + half * 16);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
+        if ((it & 1) == 0 && !mbar_wait(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
+        // this thread's 32 fields: BITS words at (64-k block parity, 32-k half) of its row
+        uint32_t w[BITS];
+        {
+          const unsigned char* src = ring_p + sp * kPStageBytes + row_in_tile * kPRowBytes +
+                                     ((it & 1) * 2 + half) * (4 * BITS);
+          if constexpr (BITS == 4) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src);
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+          } else if constexpr (BITS == 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src), u = *reinterpret_cast<const uint4*>(src + 16);
+            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; w[4] = u.x; w[5] = u.y; w[6] = u.z; w[7] = u.w;
+          } else if constexpr (BITS == 2 || BITS == 6) {
+#pragma unroll
+            for (int i = 0; i < BITS / 2; ++i) {
+              const uint2 v = *reinterpret_cast<const uint2*>(src + 8 * i);
+              w[2 * i] = v.x; w[2 * i + 1] = v.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < BITS; ++i) w[i] = *reinterpret_cast<const uint32_t*>(src + 4 * i);
+          }
+        }
+        if (it & 1) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
+        }
         uint32_t vals[16];
-        dequant32_b4(w, s_cur * 0x00010001u, b_cur * 0x00010001u, vals);
+        dequant32<BITS>(w, s_cur, b_cur, vals);
         if (pending) publish();
         if (!mbar_wait(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
@@ -283,6 +348,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   } else {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;
+    const int chalf = (warp - (2 + kDequantWarps)) >> 2;  // which half of the token columns
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
@@ -291,17 +357,26 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       tcgen05_fence_after();
       const int n = tc_.n0 + quad * 32 + lane;
       const int m0 = tc_.x_row0;
-      for (int c = 0; c < p.NT; c += 32) {
+      const int c_begin = chalf * (p.NT / 2 / 16 * 16);            // NT is a multiple of 16
+      const int c_end = chalf == 0 ? c_begin + (p.NT / 2 / 16 * 16) : p.NT;
+      for (int c = c_begin; c < c_end; c += 32) {
         uint32_t v[32];
         tcgen05_ld_x32(tmem_acc + lane_field + c, v);
         tcgen05_wait_ld();
-        if (n < p.N) {
+        const int lim = (tc_.rows < c_end ? tc_.rows : c_end) - c;  // valid columns of this chunk
+        if (n < p.N && lim > 0) {
+          if (p.dst_row == nullptr) {
+            __nv_bfloat16* yp = p.y + (size_t)(m0 + c) * p.N + n;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (c + j < tc_.rows) {
-              const int m = p.dst_row ? p.dst_row[m0 + c + j] : m0 + c + j;
-              p.y[(size_t)m * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            for (int j = 0; j < 32; ++j) {
+              if (j < lim) *yp = __float2bfloat16_rn(__uint_as_float(v[j]));
+              yp += p.N;
             }
+          } else {
+            const int* dr = p.dst_row + m0 + c;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < lim) p.y[(size_t)dr[j] * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
           }
         }
       }
@@ -345,24 +420,39 @@ int pick_nt(int64_t M) {
   return (int)(nt > 256 ? 256 : nt);
 }
 
-size_t smem_bytes(int nt) {
+size_t smem_bytes(int nt, int bits) {
   const size_t b_pitch = ((size_t)nt * 128 + 1023) & ~size_t(1023);
-  const size_t need = 1024 + kStagesB * b_pitch + (size_t)kStagesP * kTileN * 32 + sizeof(Barriers) + 64;
+  const size_t need = 1024 + kStagesB * b_pitch + (size_t)kStagesP * kTileN * 16 * bits + sizeof(Barriers) + 64;
   // More than half of an SM's shared memory: guarantees one CTA per SM, so the 512-column
   // tensor-memory allocation never has to wait for a co-resident CTA of this kernel.
   const size_t one_per_sm = 120 * 1024;
   return need > one_per_sm ? need : one_per_sm;
 }
 
+// Launches the kernel instantiated for `bits`.
+int launch_tc(int bits, int grid, size_t smem, cudaStream_t st, const CUtensorMap& map_x, const CUtensorMap& map_w,
+              const TcParams& p) {
+  int rc = B200Q_ERR_UNSUPPORTED;
+  B200Q_DISPATCH_BITS(bits, BITS, {
+    cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    qmm_tc_kernel<BITS><<<grid, kThreads, smem, st>>>(map_x, map_w, p);
+    rc = B200Q_OK;
+  });
+  if (rc != B200Q_OK) return fail(rc, "[quantized_matmul] unsupported bits %d", bits);
+  B200Q_LAUNCH_OK("qmm_tc_kernel");
+  return B200Q_OK;
+}
+
 }  // namespace
 
 bool qmm_tc_supported(const QmmArgs& a) {
-  if (a.dtype != B200Q_BF16 || !a.transpose || a.w_batched || a.batch != 1 || a.bits != 4) return false;
-  if (a.M < 1 || a.N < 1 || a.K < kBlockK || a.K % kBlockK != 0) return false;
+  if (a.dtype != B200Q_BF16 || !a.transpose || a.w_batched || a.batch != 1) return false;
+  if (a.M < 1 || a.N < 1 || a.K < 128 || a.K % 128 != 0) return false;  // packed stages hold 128 k
   if (a.K % a.group != 0) return false;
   // TMA: 16-byte aligned bases and row pitches (x rows: 2K bytes, packed rows: K/2 bytes)
   if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (reinterpret_cast<uintptr_t>(a.wq) & 15)) return false;
-  if ((a.K * 2) % 16 != 0 || (a.K / 2) % 16 != 0) return false;
+  if ((a.K * 2) % 16 != 0 || (a.K * a.bits / 8) % 16 != 0) return false;
   return true;
 }
 
@@ -387,9 +477,9 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
     if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for x failed (%d)", (int)r);
   }
   {
-    const cuuint64_t dims[2] = {(cuuint64_t)a.K / 2, (cuuint64_t)a.N};
-    const cuuint64_t strides[1] = {(cuuint64_t)a.K / 2};
-    const cuuint32_t box[2] = {32, (cuuint32_t)kTileN};
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K * a.bits / 8, (cuuint64_t)a.N};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * a.bits / 8};
+    const cuuint32_t box[2] = {(cuuint32_t)(16 * a.bits), (cuuint32_t)kTileN};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.wq), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -411,11 +501,7 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = (long long)p.n_tiles * p.m_tiles;
   const int grid = (int)(tiles < sms ? tiles : sms);
-  const size_t smem = smem_bytes(nt);
-  B200Q_CUDA_OK(cudaFuncSetAttribute(qmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  qmm_tc_kernel<<<grid, kThreads, smem, st>>>(map_x, map_w, p);
-  B200Q_LAUNCH_OK("qmm_tc_kernel");
-  return B200Q_OK;
+  return launch_tc(a.bits, grid, smem_bytes(nt, a.bits), st, map_x, map_w, p);
 }
 
 int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
@@ -434,9 +520,9 @@ int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
     if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[gather_qmm] tensor map for x failed (%d)", (int)r);
   }
   {
-    const cuuint64_t dims[2] = {(cuuint64_t)a.K / 2, (cuuint64_t)(a.E * a.N)};
-    const cuuint64_t strides[1] = {(cuuint64_t)a.K / 2};
-    const cuuint32_t box[2] = {32, (cuuint32_t)kTileN};
+    const cuuint64_t dims[2] = {(cuuint64_t)a.K * a.bits / 8, (cuuint64_t)(a.E * a.N)};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.K * a.bits / 8};
+    const cuuint32_t box[2] = {(cuuint32_t)(16 * a.bits), (cuuint32_t)kTileN};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.wq), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -461,11 +547,7 @@ int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = (long long)p.n_tiles * a.max_mtiles;  // upper bound; the kernel reads the exact count
   const int grid = (int)(tiles < sms ? tiles : sms);
-  const size_t smem = smem_bytes(nt);
-  B200Q_CUDA_OK(cudaFuncSetAttribute(qmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  qmm_tc_kernel<<<grid, kThreads, smem, st>>>(map_x, map_w, p);
-  B200Q_LAUNCH_OK("qmm_tc_kernel");
-  return B200Q_OK;
+  return launch_tc(a.bits, grid, smem_bytes(nt, a.bits), st, map_x, map_w, p);
 }
 
 size_t qmm_tc_mtile_bytes() { return sizeof(MTile); }

@@ -74,9 +74,9 @@ def test_gather_bad_index_is_flagged_not_faulted():
 
 
 # ---- sort-by-expert grouped path (bf16, 4-bit, transpose) -------------------------------
-def _moe_case(E, tokens, topk, N, K, M=1, g=64, seed=0):
+def _moe_case(E, tokens, topk, N, K, M=1, g=64, seed=0, bits=4):
     dtype = "bf16"
-    wq, s, b = O.quantize(make_w(100 + seed, (E, N, K), dtype), g, 4, dtype)
+    wq, s, b = O.quantize(make_w(100 + seed, (E, N, K), dtype), g, bits, dtype)
     x = make_x(1 + seed, (tokens, M, K), dtype)
     rng = np.random.default_rng(3 + seed)
     rhs = rng.permuted(np.tile(np.arange(E), (tokens, 1)), axis=1)[:, :topk].astype(np.uint32)
@@ -95,6 +95,19 @@ def test_gather_grouped_vs_oracle(E, tokens, topk, N, K, M, g):
     assert tuple(y.shape) == (tokens, topk, M, N)
     ref = O.gather_qmm(O.to_f32(x, dtype), wq, O.to_f32(s, dtype), O.to_f32(b, dtype), lhs.ravel(), rhs.ravel(), True,
                        g, 4, "f32")
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype).reshape(ref.shape), ref)
+    assert ok, rel
+
+
+@pytest.mark.parametrize("bits", (3, 6, 8))
+def test_gather_grouped_other_bit_widths(bits):
+    E, tokens, topk, N, K, g = 4, 40, 2, 256, 512, 64
+    dtype, wq, s, b, x, lhs, rhs = _moe_case(E, tokens, topk, N, K, 1, g, bits=bits)
+    y = mb.gather_qmm(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype),
+                      lhs_indices=torch.from_numpy(lhs.astype(np.int64)), rhs_indices=torch.from_numpy(rhs.astype(np.int64)),
+                      group_size=g, bits=bits)
+    ref = O.gather_qmm(O.to_f32(x, dtype), wq, O.to_f32(s, dtype), O.to_f32(b, dtype), lhs.ravel(), rhs.ravel(), True,
+                       g, bits, "f32")
     ok, rel = qmm_close(O.to_f32(from_torch(y), dtype).reshape(ref.shape), ref)
     assert ok, rel
 

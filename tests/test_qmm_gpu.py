@@ -170,11 +170,22 @@ print("bulk-ok")
 
 
 # ---- prefill path (TMA + tcgen05 + TMEM) -------------------------------------------------
-@pytest.mark.parametrize("M,N,K,g", [(64, 128, 64, 64), (17, 128, 128, 32), (33, 256, 256, 128), (256, 256, 512, 64),
+@pytest.mark.parametrize("M,N,K,g", [(64, 128, 128, 64), (17, 128, 128, 32), (33, 256, 256, 128), (256, 256, 512, 64),
                                      (300, 384, 1024, 128), (100, 200, 256, 64), (512, 1024, 4096, 64),
-                                     (257, 130, 192, 32)])
+                                     (257, 130, 384, 32)])
 def test_tcgen05_shapes(M, N, K, g):
     run_case("bf16", M, N, K, g, 4, seed=M + K, expect_kernel=("qmm_tcgen05",))
+
+
+@pytest.mark.parametrize("bits", (2, 3, 5, 6, 8))
+@pytest.mark.parametrize("g", (32, 64, 128))
+def test_tcgen05_all_bit_widths(bits, g):
+    run_case("bf16", 96, 200, 640, g, bits, seed=bits + g, expect_kernel=("qmm_tcgen05",))
+    run_case("bf16", 512, 256, 1024, g, bits, seed=bits, expect_kernel=("qmm_tcgen05",))
+
+
+def test_ragged_k_falls_back_to_generic():
+    run_case("bf16", 40, 96, 192, 32, 4, seed=1, expect_kernel=("qmm_generic",))
 
 
 def test_tcgen05_prefill_full_size_sampled_rows():
