@@ -24,7 +24,11 @@
  *     with the matching *_workspace_bytes() query.  The first bytes of a workspace
  *     hold self-cleaning counters: zero the workspace once after allocating it
  *     (b200q_workspace_init) and never share one workspace between two calls that
- *     may overlap on the GPU;
+ *     may overlap on the GPU.  b200q_qmm leaves its workspace zeroed again;
+ *     b200q_gather_qmm uses everything but the last 16 bytes as plain scratch and
+ *     leaves arbitrary data there (it needs only those last 16 bytes to be zero), so
+ *     keep a separate workspace for it or re-initialise before reusing the memory
+ *     for b200q_qmm;
  *   - return value: 0 on success; negative = rejected on the host before any launch
  *     (see the B200Q_ERR_* codes; the text of the last error of the calling thread is
  *     returned by b200q_last_error()).  B200Q_ERR_INVALID_ARGUMENT corresponds to the

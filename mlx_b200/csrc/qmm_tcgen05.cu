@@ -8,13 +8,22 @@
 // operand that has to be dequantised (W) is the 128-row A operand and is re-used by up
 // to 256 tokens per instruction, and the operand that streams unchanged (x) is B.
 //
-//   TMA  --packed W tile [128 rows x 64 k]-->  smem ring P
+//   thread A: TMA  --packed W tile [128 rows x 128 k, 16*bits bytes per row]-->  smem ring P
 //   8 dequant warps: one thread per weight row (= one TMEM lane): unpack 32 k with
 //        shift/lop3/prmt, apply s*q+b in bf16x2, tcgen05.st into the A ring in TMEM
-//   TMA  --x tile [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
+//   thread B: TMA  --x tile [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
 //   1 thread: tcgen05.mma.kind::f16 (A from TMEM, B from smem descriptors), fp32
 //        accumulator [128 lanes x NT columns] in TMEM, tcgen05.commit on mbarriers
-//   4 epilogue warps: tcgen05.ld the accumulator, round to bf16, store y (transposed)
+//   8 epilogue warps (two per TMEM lane quadrant, half of the token columns each):
+//        tcgen05.ld the accumulator, round to bf16, store y (transposed; scattered through
+//        a row table in grouped mode)
+//
+// The two TMA streams have a thread each: behind the x-tile waits the packed tiles would
+// arrive late and starve the dequant warps.
+//
+// Grouped mode (gather_qmm): a device-side table lists (expert, first row, valid rows) for
+// every NT-row slice of the expert-sorted activations; the weight tensor map spans the
+// stacked experts [E*N, K*bits/8].
 //
 // TMEM columns (512 allocated): [0, 256) accumulator, [256, 512) A ring of 8 stages
 // (64 k of bf16 = 32 columns each).  One CTA per SM (persistent), tiles are taken
@@ -41,7 +50,8 @@ constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kDequantWarps = 8;
 constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each drains half of the columns
-constexpr int kThreads = 32 * (2 + kDequantWarps + kEpilogueWarps);  // 576
+constexpr int kProducerPWarp = 2 + kDequantWarps + kEpilogueWarps;  // last warp
+constexpr int kThreads = 32 * (3 + kDequantWarps + kEpilogueWarps);  // 608
 
 using namespace tc;
 
@@ -195,6 +205,20 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef B200Q_PROFILE
+  // Profile builds (plain mode only): CTA 0 leaves per-role wait cycles / 16 in the 256 bytes
+  // before the status word; the caller's workspace must have that room.
+  uint32_t* dbg = p.status - 64;
+  long long pw0 = 0, pw1 = 0, pw2 = 0, pt = 0;
+  const long long prof_entry = clock64();
+#define TC_T0() pt = clock64()
+#define TC_ACC(v) v += clock64() - pt
+#define TC_OUT(slot, v) if (blockIdx.x == 0 && lane == 0 && p.mtiles == nullptr) dbg[slot] = (uint32_t)((v) >> 4)
+#else
+#define TC_T0()
+#define TC_ACC(v)
+#define TC_OUT(slot, v)
+#endif
   const int kblocks = p.K / kBlockK;
   const int total_tiles = p.mtiles ? *p.n_mtiles * p.n_tiles : p.n_tiles * p.m_tiles;
 
@@ -219,26 +243,45 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   const uint32_t tmem_a = tmem_base + kAccCols;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer: x tiles (B ring)
     if (lane == 0) {
       uint32_t it = 0;  // k-block counter across tiles
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc_ = tile_coord(p, tile);
+        bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t itp = it >> 1;  // packed stages advance every second k-block (kblocks is even)
-          const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
           const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
-          if ((it & 1) == 0) {
-            if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) break;
-            mbar_expect_tx(smem_u32(&bars->full_p[sp]), kPStageBytes);
-            tma_load_2d(smem_u32(ring_p + sp * kPStageBytes), &map_w, (kb >> 1) * kPRowBytes, tc_.w_row0,
-                        smem_u32(&bars->full_p[sp]));
-          }
-          if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) break;
+          TC_T0();
+          if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) { ok = false; break; }
+          TC_ACC(pw1);
           mbar_expect_tx(smem_u32(&bars->full_b[sb]), b_stage_bytes);
           tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tc_.x_row0, smem_u32(&bars->full_b[sb]));
         }
+        if (!ok) break;
       }
+      TC_OUT(1, pw1); TC_OUT(2, clock64() - prof_entry);
+    }
+  } else if (warp == kProducerPWarp) {
+    // ------------------------------------------------------------ TMA producer: packed W tiles (P ring).
+    // A separate thread: behind the x-tile waits of the other producer the packed tiles would
+    // arrive late and starve the dequant warps.
+    if (lane == 0) {
+      uint32_t itp = 0;  // packed stages advance every second k-block (kblocks is even)
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const TileCoord tc_ = tile_coord(p, tile);
+        bool ok = true;
+        for (int kp = 0; kp < kblocks / 2; ++kp, ++itp) {
+          const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
+          TC_T0();
+          if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) { ok = false; break; }
+          TC_ACC(pw0);
+          mbar_expect_tx(smem_u32(&bars->full_p[sp]), kPStageBytes);
+          tma_load_2d(smem_u32(ring_p + sp * kPStageBytes), &map_w, kp * kPRowBytes, tc_.w_row0,
+                      smem_u32(&bars->full_p[sp]));
+        }
+        if (!ok) break;
+      }
+      TC_OUT(0, pw0);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -246,14 +289,20 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       const uint32_t idesc = make_idesc(p.NT);
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        TC_T0();
         if (!mbar_wait(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
+        TC_ACC(pw2);
         tcgen05_fence_after();
         bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
           const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
+          TC_T0();
           if (!mbar_wait(smem_u32(&bars->full_a[sa]), pa, abort_flag)) { ok = false; break; }
+          TC_ACC(pw0);
+          TC_T0();
           if (!mbar_wait(smem_u32(&bars->full_b[sb]), pb, abort_flag)) { ok = false; break; }
+          TC_ACC(pw1);
           tcgen05_fence_after();
           const uint32_t b_addr = smem_u32(ring_b + sb * b_stage_pitch);
 #pragma unroll
@@ -267,6 +316,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         if (!ok) break;
         tcgen05_commit(smem_u32(&bars->acc_full));
       }
+      TC_OUT(4, pw0); TC_OUT(5, pw1); TC_OUT(6, pw2); TC_OUT(7, clock64() - prof_entry);
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------------------------------------ dequant: one thread per weight row
@@ -307,7 +357,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           s_next = __ldg(sc + g);
           b_next = __ldg(bi + g);
         }
+        TC_T0();
         if ((it & 1) == 0 && !mbar_wait(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
+        TC_ACC(pw0);
         // this thread's 32 fields: BITS words at (64-k block parity, 32-k half) of its row
         uint32_t w[BITS];
         {
@@ -330,22 +382,30 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             for (int i = 0; i < BITS; ++i) w[i] = *reinterpret_cast<const uint32_t*>(src + 4 * i);
           }
         }
-        if (it & 1) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
-        }
         uint32_t vals[16];
         dequant32<BITS>(w, s_cur, b_cur, vals);
+        TC_T0();
         if (pending) publish();
+        TC_ACC(pw1);
+        TC_T0();
         if (!mbar_wait(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
+        TC_ACC(pw2);
         tcgen05_fence_after();
         tcgen05_st_x16(tmem_a + lane_field + sa * 32 + half * 16, vals);
         pending = true;
         pending_sa = sa;
+        // The packed stage is released only here, after the store that consumes the unpacked
+        // registers has been issued: the shared-memory reads above have then returned for every
+        // lane, so the refill of the stage cannot overtake them.
+        if (it & 1) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
+        }
       }
     }
     if (pending) publish();
-  } else {
+    if (warp == 2) { TC_OUT(8, pw0); TC_OUT(9, pw1); TC_OUT(10, pw2); TC_OUT(11, clock64() - prof_entry); }
+  } else if (warp < kProducerPWarp) {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;
     const int chalf = (warp - (2 + kDequantWarps)) >> 2;  // which half of the token columns
@@ -353,7 +413,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       const TileCoord tc_ = tile_coord(p, tile);
+      TC_T0();
       if (!mbar_wait(smem_u32(&bars->acc_full), tcount & 1, abort_flag)) break;
+      TC_ACC(pw0);
       tcgen05_fence_after();
       const int n = tc_.n0 + quad * 32 + lane;
       const int m0 = tc_.x_row0;
@@ -384,6 +446,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
     }
+    if (warp == 2 + kDequantWarps) { TC_OUT(12, pw0); TC_OUT(13, clock64() - prof_entry); }
   }
 
   // ---- teardown: everyone meets, then the allocating warp returns the tensor memory

@@ -491,11 +491,13 @@ qmv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const QtcParams p) {
         for (int c = first_owner; c <= last_owner; ++c) {
           const int cu0 = (int)((long long)c * T / G);
           const int which = tile == cu0 / p.chunks ? 0 : 1;
-          const float4* gp = reinterpret_cast<const float4*>(p.partial + (((size_t)c * 2 + which) * kRows + r) * 16);
+          float4* gp = reinterpret_cast<float4*>(p.partial + (((size_t)c * 2 + which) * kRows + r) * 16);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float4 v = __ldcg(gp + q);
             sum[4 * q] += v.x; sum[4 * q + 1] += v.y; sum[4 * q + 2] += v.z; sum[4 * q + 3] += v.w;
+            // leave the slot zeroed: the workspace is shared with kernels whose accumulators start at zero
+            __stcg(gp + q, make_float4(0.0f, 0.0f, 0.0f, 0.0f));
           }
         }
         if (n < p.N) {

@@ -45,13 +45,17 @@ def _as_u32(w: torch.Tensor, tag: str) -> torch.Tensor:
 
 
 class _Workspaces:
-    """One zero-initialised scratch buffer per (device, stream); it only grows."""
+    """One zero-initialised scratch buffer per (device, stream, operator); it only grows.
+
+    quantized_matmul and gather_qmm keep separate buffers: the matmul kernels rely on
+    counters that start at zero and are left at zero, while gather_qmm uses its buffer as
+    plain scratch (sorted indices, tile table, gathered rows)."""
 
     def __init__(self):
         self._bufs = {}
 
-    def get(self, dev: torch.device, nbytes: int) -> torch.Tensor:
-        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    def get(self, dev: torch.device, nbytes: int, op: str) -> torch.Tensor:
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream, op)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < nbytes:
             with torch.cuda.device(dev):
@@ -252,7 +256,7 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
     with torch.cuda.device(dev):
         y = torch.empty(out_lead + (M, N), dtype=dtype, device=dev)
         need = lib.b200q_qmm_workspace_bytes(_DT[dtype], batch, M, N, K, group_size, bits, int(transpose))
-        ws = _workspaces.get(dev, need)
+        ws = _workspaces.get(dev, need, "qmm")
         rc = lib.b200q_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(y), _DT[dtype], batch, M, N, K,
                            group_size, bits, int(transpose), w_stride, _ptr(ws), ws.numel(), _stream(x))
     _lib.check(rc)
@@ -307,7 +311,7 @@ def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: O
         y = torch.empty(idx_shape + (M, N), dtype=out_type, device=dev)
         need = lib.b200q_gather_qmm_workspace_bytes(_DT[out_type], n_idx, x_batch, E, M, N, K, group_size, bits,
                                                     int(transpose))
-        ws = _workspaces.get(dev, need)
+        ws = _workspaces.get(dev, need, "gather")
         rc = lib.b200q_gather_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(lhs32), _ptr(rhs32), n_idx,
                                   _ptr(y), _DT[out_type], x_batch, E, M, N, K, group_size, bits, int(transpose),
                                   flags, _ptr(ws), ws.numel(), _stream(x))

@@ -66,7 +66,7 @@ def test_gather_bad_index_is_flagged_not_faulted():
                       lhs_indices=torch.tensor([0, 1, 2]), rhs_indices=torch.tensor([0, 9, 1]))
     torch.cuda.synchronize()
     assert bool((y[1] == 0).all()) and bool((y[0] != 0).any()) and bool((y[2] != 0).any())
-    ws = ops._workspaces.get(x.device, 0)
+    ws = ops._workspaces.get(x.device, 0, "gather")
     st = (ctypes.c_uint32 * 4)()
     rc = _lib.load().b200q_read_status(ctypes.c_void_p(ws.data_ptr()), ws.numel(),
                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), st)
@@ -146,7 +146,7 @@ def test_gather_grouped_bad_index_flagged():
                       lhs_indices=torch.from_numpy(lhs.astype(np.int64)), rhs_indices=torch.from_numpy(rhs.astype(np.int64)))
     torch.cuda.synchronize()
     assert bool((y[5, 1] == 0).all()) and bool((y[5, 0] != 0).any())
-    ws = ops._workspaces.get(y.device, 0)
+    ws = ops._workspaces.get(y.device, 0, "gather")
     st = (ctypes.c_uint32 * 4)()
     rc = _lib.load().b200q_read_status(ctypes.c_void_p(ws.data_ptr()), ws.numel(),
                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), st)
@@ -156,3 +156,19 @@ def test_gather_grouped_bad_index_flagged():
     got = O.to_f32(from_torch(y), dtype)[good]
     ok, rel = qmm_close(got.reshape(ref.shape), ref)
     assert ok, rel
+
+
+def test_gather_then_decode_on_one_stream():
+    """A grouped gather_qmm followed by a decode-sized quantized_matmul on the same stream: the
+    gather's scratch (sorted indices, tile table, gathered rows) must not leak into the counters
+    the decode kernel expects to find at zero."""
+    E, tokens, topk, N, K, g = 4, 48, 2, 256, 512, 64
+    dtype, wq, s, b, x, lhs, rhs = _moe_case(E, tokens, topk, N, K, 1, g)
+    wq_t, s_t, b_t, x_t = u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype), to_torch(x, dtype)
+    for _ in range(2):
+        mb.gather_qmm(x_t, wq_t, s_t, b_t, lhs_indices=torch.from_numpy(lhs.astype(np.int64)),
+                      rhs_indices=torch.from_numpy(rhs.astype(np.int64)), group_size=g, bits=4)
+        y = mb.quantized_matmul(x_t[:3, 0], wq_t.view(torch.int32)[1].view(torch.uint32), s_t[1], b_t[1], group_size=g, bits=4)
+        ref = O.qmm_f32_from(x[:3, 0], wq[1], s[1], b[1], dtype, transpose=True, group_size=g, bits=4)
+        ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), ref)
+        assert ok, rel

@@ -153,7 +153,10 @@ sys.path.insert(0, "tests")
 import torch, oracle as O, mlx_b200 as mb
 from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch
 for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048, 32), (13, 4104, 4096, 128), (5, 520, 8192, 64)]:
-    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4) == "qmv_" + sys.argv[1]
+    # the last shape exceeds the tensor-memory variant's shared-memory budget and falls back to the
+    # default kernel ON THE SAME WORKSPACE: every kernel must leave the workspace zeroed
+    name = mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4)
+    assert name == "qmv_" + sys.argv[1] or (K == 8192 and name == "qmv_mma"), name
     wq, s, b = O.quantize(make_w(N, (N, K), "bf16"), g, 4, "bf16")
     x = make_x(M, (M, K), "bf16")
     ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
