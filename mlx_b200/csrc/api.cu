@@ -32,7 +32,7 @@ void count_launch(int n) { g_launches += (uint64_t)n; }
 
 namespace {
 
-enum class Path { QmvTc, QmvBulk, Qmv, Tc, Generic };
+enum class Path { QmvStream, QmvTc, QmvBulk, Qmv, Tc, Generic };
 
 int check_qmm_args(const char* tag, const QmmArgs& a) {
   if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
@@ -54,12 +54,13 @@ int check_qmm_args(const char* tag, const QmmArgs& a) {
   return B200Q_OK;
 }
 
-// B200Q_QMV_IMPL=bulk|mma forces one of the two decode kernels (testing and tuning).
+// B200Q_QMV_IMPL=stream|bulk|mma|tc forces one of the decode kernels where it supports the shape
+// (testing and tuning).
 int qmv_override() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_QMV_IMPL");
-    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : 0)));
+    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : (strcmp(e, "stream") == 0 ? 4 : 0))));
   }
   return v;
 }
@@ -76,9 +77,9 @@ bool force_tc() {
 Path choose(const QmmArgs& a) {
   const int ov = qmv_override();
   if (force_tc() && qmm_tc_supported(a)) return Path::Tc;  // tuning aid: tensor-memory path for any M
-  // The register-path kernel is currently the faster of the two decode kernels.
   if (ov == 3 && qmv_tc_supported(a)) return Path::QmvTc;
   if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
+  if (qmv_stream_supported(a) && (ov == 4 || (ov == 0 && qmv_stream_profitable(a)))) return Path::QmvStream;
   if (qmv_mma_supported(a)) return Path::Qmv;
   if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
   if (qmm_tc_supported(a)) return Path::Tc;
@@ -110,6 +111,7 @@ int run_qmm(const QmmArgs& a, cudaStream_t st) {
   if (!a.x || !a.wq || !a.scales || !a.biases || !a.y)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null pointer");
   switch (choose(a)) {
+    case Path::QmvStream: return qmv_stream(a, st);
     case Path::QmvTc: return qmv_tc(a, st);
     case Path::QmvBulk: return qmv_bulk(a, st);
     case Path::Qmv: return qmv_mma(a, st);
@@ -139,6 +141,8 @@ extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M,
   q = q > qb ? q : qb;
   const size_t qt = qmv_tc_workspace_bytes(a);
   q = q > qt ? q : qt;
+  const size_t qs = qmv_stream_workspace_bytes(a);
+  q = q > qs ? q : qs;
   size_t t = qmm_tc_workspace_bytes(a);
   need = q > t ? q : t;
   return (need + 255) / 256 * 256;
@@ -160,6 +164,7 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
                         group_size, bits, transpose, 0, nullptr, 0);
   if (check_qmm_args("quantized_matmul", a)) return "invalid";
   switch (choose(a)) {
+    case Path::QmvStream: return "qmv_stream";
     case Path::QmvTc: return "qmv_tc";
     case Path::QmvBulk: return "qmv_bulk";
     case Path::Qmv: return "qmv_mma";

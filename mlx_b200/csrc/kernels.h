@@ -58,6 +58,12 @@ bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a);
 int qmv_mma(const QmmArgs& a, cudaStream_t st);
 
+// qmv_stream.cu : decode path for 4-bit weights (TMA ring, ldmatrix, exact factorised form)
+bool qmv_stream_supported(const QmmArgs& a);
+bool qmv_stream_profitable(const QmmArgs& a);   // large enough to beat qmv_mma
+size_t qmv_stream_workspace_bytes(const QmmArgs& a);
+int qmv_stream(const QmmArgs& a, cudaStream_t st);
+
 // qmv_bulk.cu : decode path for 4-bit weights (bulk-copy staged, exact factorised form)
 bool qmv_bulk_supported(const QmmArgs& a);
 size_t qmv_bulk_workspace_bytes(const QmmArgs& a);

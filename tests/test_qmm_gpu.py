@@ -59,13 +59,13 @@ def test_golden_qmm(dtype, g, bits):
 @pytest.mark.parametrize("g", (32, 64, 128))
 @pytest.mark.parametrize("M", (1, 3, 8, 9, 16))
 def test_qmv_all_widths(bits, g, M):
-    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_stream", "qmv_mma", "qmv_bulk"))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 14336, 4096), (7, 67, 256), (2, 8, 128), (16, 1000, 2048),
                                    (5, 28672, 8192), (13, 4104, 4096), (16, 24, 128)])
 def test_qmv_shapes_4bit(M, N, K):
-    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_stream", "qmv_mma", "qmv_bulk"))
 
 
 def test_qmv_repeated_calls_reuse_scratch():
@@ -140,7 +140,7 @@ def test_mixed_dtype_promotes_to_float32():
     assert ok, rel
 
 
-@pytest.mark.parametrize("impl", ("bulk", "tc"))
+@pytest.mark.parametrize("impl", ("bulk", "tc", "mma", "stream"))
 def test_qmv_alternative_kernels_in_subprocess(impl):
     """The bulk-copy staged (mma.sync) and the tensor-memory (tcgen05) decode kernels are selected
     with B200Q_QMV_IMPL=bulk|tc; run a few shapes through each in a child process (the override is
