@@ -164,8 +164,49 @@ int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const void* scale
                             int bits, void* stream);
 
 /*
+ * N-sharded linear with the all_gather fused into the matmul epilogue.  Replaces the pair
+ * QuantizedAllToShardedLinear.__call__ + all_gather of the reference
+ * (python/mlx/nn/layers/distributed.py:357-455, mlx/distributed/ops.cpp:62-84,
+ * mlx/distributed/nccl/nccl.cpp:346-358): rank r holds rows [r*N/R, (r+1)*N/R) of
+ * wq / scales / biases, x is replicated, and every rank ends up with the full [M, N].
+ * Instead of a collective after the kernel, the kernel stores every finished output
+ * tile straight into the output buffer of EVERY rank (peer stores over NVLink):
+ *   y_peers[q][m * ld + col0 + n] = y_local[m][n]   for q < n_peers, n < N_local
+ * y_peers are device pointers valid on the current device (the local buffer and the
+ * peer-mapped buffers of the other ranks, see b200q_ipc_*), ld = N (row pitch of the
+ * full output), col0 = rank * N_local.  bfloat16, transpose form only; other problems
+ * return B200Q_ERR_UNSUPPORTED (use b200q_qmm and a collective).
+ *
+ * Completion across ranks uses one 32-bit flag word per rank that only ever grows:
+ * after b200q_qmm_sharded, b200q_peer_signal adds 1 to the flag of every rank (system
+ * scope, ordered after all earlier work on `stream`); b200q_peer_wait makes `stream`
+ * wait until the local flag has reached `expected` (= step * world size).  The wait is
+ * bounded (about one second): when it runs out, code 6 is stored in status[0] (device
+ * memory, 4 words, e.g. the status word of the workspace) and the stream continues.
+ */
+int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                      void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
+                      int64_t M, int64_t N_local, int64_t K, int group_size, int bits, void* ws,
+                      size_t ws_bytes, void* stream);
+int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, void* stream);
+int b200q_peer_wait(const uint32_t* flag_local, uint32_t expected, uint32_t* status, void* stream);
+
+/*
+ * Set-up helpers for the peer buffers (not capture-safe, they allocate): a buffer that
+ * other processes on the same machine can map (cudaMalloc + cudaIpcGetMemHandle), and
+ * the mapping of another process's buffer into this one (cudaIpcOpenMemHandle with lazy
+ * peer access).  `handle` is the 64-byte CUDA IPC handle, to be exchanged by the caller
+ * (e.g. torch.distributed.all_gather_object).
+ */
+int b200q_ipc_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+int b200q_ipc_open(const unsigned char handle[64], void** ptr);
+int b200q_ipc_close(void* ptr);
+int b200q_ipc_free(void* ptr);
+
+/*
  * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
- * launch for this problem ("qmv_bulk", "qmv_mma", "qmm_tcgen05", "qmm_generic").
+ * launch for this problem ("qmv_mma", "qmv_stream", "qmv_bulk", "qmv_tc", "qmm_tcgen05",
+ * "qmm_generic").
  */
 const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
                                   int group_size, int bits, int transpose);

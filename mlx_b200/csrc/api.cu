@@ -173,6 +173,105 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
   }
 }
 
+// ---------------------------------------------------------------- N-sharded output with peer stores
+namespace b200q {
+namespace peer {
+__global__ void peer_signal_kernel(uint32_t* f0, uint32_t* f1, uint32_t* f2, uint32_t* f3, uint32_t* f4, uint32_t* f5,
+                                   uint32_t* f6, uint32_t* f7, int n) {
+  uint32_t* f[kMaxPeers] = {f0, f1, f2, f3, f4, f5, f6, f7};
+  // everything enqueued before this kernel on the stream (the peer stores of the matmul) has
+  // completed; the fence orders it before the flag updates for observers on other GPUs
+  __threadfence_system();
+  for (int q = 0; q < n; ++q) atomicAdd_system(f[q], 1u);
+}
+__global__ void peer_wait_kernel(const uint32_t* flag, uint32_t expected, uint32_t* status) {
+  const long long t0 = clock64();
+  const long long limit = 2000000000ll;  // about one second of SM clocks
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if ((int32_t)(v - expected) >= 0) break;
+    if (clock64() - t0 > limit) {
+      atomicMax(&status[0], 6u);
+      status[1] = v;
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+}  // namespace peer
+}  // namespace b200q
+
+extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                                 void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M,
+                                 int64_t N_local, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
+                                 void* stream) {
+  if (!y_peers || n_peers < 1 || n_peers > kMaxPeers)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] between 1 and %d output buffers are supported (got %d)", kMaxPeers, n_peers);
+  if (ld < N_local || col0 < 0 || col0 + N_local > ld)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] columns [%lld, %lld) do not fit a row pitch of %lld",
+                (long long)col0, (long long)(col0 + N_local), (long long)ld);
+  QmmArgs a = make_args(x, wq, scales, biases, y_peers[0], dtype, 1, M, N_local, K, group_size, bits, 1, 0, ws, ws_bytes);
+  if (int rc = check_qmm_args("quantized_matmul_sharded", a)) return rc;
+  for (int q = 0; q < n_peers; ++q) {
+    if (!y_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null output buffer %d", q);
+    a.peers.y[q] = y_peers[q];
+  }
+  a.peers.n = n_peers; a.peers.ld = ld; a.peers.col0 = col0;
+  if (a.M == 0 || a.N == 0) return B200Q_OK;
+  if (!x || !wq || !scales || !biases) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a.K > 0 && qmv_mma_supported(a)) return qmv_mma(a, st);
+  if (a.K > 0 && qmm_tc_supported(a)) return qmm_tc(a, st);
+  return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
+}
+
+extern "C" int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, void* stream) {
+  if (!flag_peers || n_peers < 1 || n_peers > kMaxPeers)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_signal] between 1 and %d flags are supported (got %d)", kMaxPeers, n_peers);
+  uint32_t* f[kMaxPeers] = {};
+  for (int q = 0; q < n_peers; ++q) {
+    if (!flag_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_signal] null flag %d", q);
+    f[q] = flag_peers[q];
+  }
+  peer::peer_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], n_peers);
+  B200Q_LAUNCH_OK("peer_signal_kernel");
+  return B200Q_OK;
+}
+
+extern "C" int b200q_peer_wait(const uint32_t* flag_local, uint32_t expected, uint32_t* status, void* stream) {
+  if (!flag_local || !status) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_wait] null pointer");
+  peer::peer_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag_local, expected, status);
+  B200Q_LAUNCH_OK("peer_wait_kernel");
+  return B200Q_OK;
+}
+
+extern "C" int b200q_ipc_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+  if (!ptr || !handle || bytes == 0) return fail(B200Q_ERR_INVALID_ARGUMENT, "[ipc_alloc] bad argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+  B200Q_CUDA_OK(cudaMalloc(ptr, bytes));
+  B200Q_CUDA_OK(cudaMemset(*ptr, 0, bytes));
+  cudaIpcMemHandle_t h;
+  B200Q_CUDA_OK(cudaIpcGetMemHandle(&h, *ptr));
+  memcpy(handle, &h, 64);
+  return B200Q_OK;
+}
+extern "C" int b200q_ipc_open(const unsigned char handle[64], void** ptr) {
+  if (!ptr || !handle) return fail(B200Q_ERR_INVALID_ARGUMENT, "[ipc_open] bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  B200Q_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return B200Q_OK;
+}
+extern "C" int b200q_ipc_close(void* ptr) {
+  if (ptr) B200Q_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return B200Q_OK;
+}
+extern "C" int b200q_ipc_free(void* ptr) {
+  if (ptr) B200Q_CUDA_OK(cudaFree(ptr));
+  return B200Q_OK;
+}
+
 extern "C" int b200q_workspace_init(void* ws, size_t ws_bytes, void* stream) {
   if (ws_bytes == 0) return B200Q_OK;
   if (!ws) return fail(B200Q_ERR_INVALID_ARGUMENT, "[workspace_init] null workspace");

@@ -8,6 +8,16 @@
 
 namespace b200q {
 
+// Output replicated into the buffers of several GPUs (N-sharded linear with the all_gather
+// fused into the epilogue): element (m, n) of the local [M, N] result goes to
+// y[q][m * ld + col0 + n] for every q < n.  n == 0 means the plain output QmmArgs::y.
+constexpr int kMaxPeers = 8;
+struct PeerOut {
+  void* y[kMaxPeers];
+  int n;
+  int64_t ld, col0;
+};
+
 struct QmmArgs {
   const void* x;
   const uint32_t* wq;
@@ -22,6 +32,7 @@ struct QmmArgs {
   bool w_batched;  // wq/scales/biases hold `batch` matrices
   void* ws;
   size_t ws_bytes;
+  PeerOut peers;
 };
 
 // Grouped (mixture-of-experts) problem for the tensor-core kernel: activation rows sorted by

@@ -89,6 +89,10 @@ struct TcParams {
   const __nv_bfloat16* scales;
   const __nv_bfloat16* biases;
   __nv_bfloat16* y;
+  // plain mode: output buffers (one, or one per GPU of an N-sharded layer), row pitch and first column
+  __nv_bfloat16* y_out[kMaxPeers];
+  int n_out;
+  long long ld, col0;
   uint32_t* status;
   int M, N, K;
   int NT;            // tokens per tile (multiple of 16, <= 256)
@@ -428,11 +432,13 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         const int lim = (tc_.rows < c_end ? tc_.rows : c_end) - c;  // valid columns of this chunk
         if (n < p.N && lim > 0) {
           if (p.dst_row == nullptr) {
-            __nv_bfloat16* yp = p.y + (size_t)(m0 + c) * p.N + n;
+            for (int q = 0; q < p.n_out; ++q) {
+              __nv_bfloat16* yp = p.y_out[q] + (size_t)(m0 + c) * p.ld + p.col0 + n;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < lim) *yp = __float2bfloat16_rn(__uint_as_float(v[j]));
-              yp += p.N;
+              for (int j = 0; j < 32; ++j) {
+                if (j < lim) *yp = __float2bfloat16_rn(__uint_as_float(v[j]));
+                yp += p.ld;
+              }
             }
           } else {
             const int* dr = p.dst_row + m0 + c;
@@ -553,6 +559,12 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
   p.scales = (const __nv_bfloat16*)a.scales;
   p.biases = (const __nv_bfloat16*)a.biases;
   p.y = (__nv_bfloat16*)a.y;
+  if (a.peers.n > 0) {
+    p.n_out = a.peers.n; p.ld = a.peers.ld; p.col0 = a.peers.col0;
+    for (int q = 0; q < a.peers.n; ++q) p.y_out[q] = (__nv_bfloat16*)a.peers.y[q];
+  } else {
+    p.n_out = 1; p.ld = a.N; p.col0 = 0; p.y_out[0] = (__nv_bfloat16*)a.y;
+  }
   p.status = reinterpret_cast<uint32_t*>(static_cast<char*>(a.ws) + a.ws_bytes - kStatusBytes);
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.NT = nt;

@@ -162,7 +162,9 @@ struct QmvParams {
   const uint32_t* wq;
   const __nv_bfloat16* scales;
   const __nv_bfloat16* biases;
-  __nv_bfloat16* y;
+  __nv_bfloat16* y[kMaxPeers];  // output buffers (one, or one per GPU of an N-sharded layer)
+  int n_out;
+  long long ld, col0;  // row pitch and first column of this result inside every output buffer
   uint32_t* counters;  // [n_row_blocks]
   float* partial;      // [n_row_blocks][16*RT rows][8*MT tokens]
   int M, N, K;
@@ -366,8 +368,10 @@ qmv_mma_kernel(const QmvParams p) {
     if (full) {
       for (int i = tid; i < ROWS * TOKS; i += kThreads) {
         const int tk = i / ROWS, r = i % ROWS;
-        if (tk < p.M && n0 + r < p.N)
-          p.y[(int64_t)tk * p.N + n0 + r] = __float2bfloat16_rn(tb[r * TOKS + tk]);
+        if (tk < p.M && n0 + r < p.N) {
+          const __nv_bfloat16 o = __float2bfloat16_rn(tb[r * TOKS + tk]);
+          for (int q = 0; q < p.n_out; ++q) p.y[q][(int64_t)tk * p.ld + p.col0 + n0 + r] = o;
+        }
       }
       continue;
     }
@@ -392,7 +396,10 @@ qmv_mma_kernel(const QmvParams p) {
         const int tk = i / ROWS, r = i % ROWS;
         const float v = __ldcg(&gp[r * TOKS + tk]);
         __stcg(&gp[r * TOKS + tk], 0.0f);
-        if (tk < p.M && n0 + r < p.N) p.y[(int64_t)tk * p.N + n0 + r] = __float2bfloat16_rn(v);
+        if (tk < p.M && n0 + r < p.N) {
+          const __nv_bfloat16 o = __float2bfloat16_rn(v);
+          for (int q = 0; q < p.n_out; ++q) p.y[q][(int64_t)tk * p.ld + p.col0 + n0 + r] = o;
+        }
       }
     }
     __syncthreads();
@@ -441,7 +448,12 @@ QmvPlan make_plan(const QmmArgs& a) {
   p.wq = a.wq;
   p.scales = (const __nv_bfloat16*)a.scales;
   p.biases = (const __nv_bfloat16*)a.biases;
-  p.y = (__nv_bfloat16*)a.y;
+  if (a.peers.n > 0) {
+    p.n_out = a.peers.n; p.ld = a.peers.ld; p.col0 = a.peers.col0;
+    for (int q = 0; q < a.peers.n; ++q) p.y[q] = (__nv_bfloat16*)a.peers.y[q];
+  } else {
+    p.n_out = 1; p.ld = a.N; p.col0 = 0; p.y[0] = (__nv_bfloat16*)a.y;
+  }
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ksteps = ksteps;
   p.n_row_blocks = nrb;

@@ -98,3 +98,105 @@ def all_gather_columns(y_local: torch.Tensor, group=None, world: Optional[int] =
 def expert_bounds(n_experts: int, rank: int, world: int) -> Tuple[int, int]:
     """Experts owned by `rank` in the expert-parallel layout (contiguous blocks)."""
     return shard_bounds(n_experts, rank, world)
+
+
+# ---------------------------------------------------------------------------------------------
+# all_gather fused into the matmul epilogue: every rank's kernel stores its [M, N/R] block
+# straight into the [M, N] output buffer of every rank (peer stores over NVLink), so no
+# collective runs after the kernel; a per-rank flag word says when all blocks have landed.
+# ---------------------------------------------------------------------------------------------
+import ctypes
+
+from . import _lib
+
+
+class _DevMem:
+    """Exposes a raw device pointer to torch through __cuda_array_interface__ (as uint16)."""
+
+    def __init__(self, ptr: int, n_u16: int):
+        self.__cuda_array_interface__ = {"shape": (n_u16,), "typestr": "<u2", "data": (ptr, False), "version": 2}
+
+
+class PeerOutput:
+    """Two alternating [m_max, n_total] bf16 output buffers per rank, mapped into every rank of
+    `group` with CUDA IPC, plus one arrival flag per rank.  Collective constructor (all ranks of
+    the group call it).  Ranks must be processes on one machine, one GPU each."""
+
+    N_BUF = 2
+
+    def __init__(self, m_max: int, n_total: int, group=None):
+        self.lib = _lib.load()
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks can share output buffers")
+        self.m_max, self.n_total = m_max, n_total
+        self.buf_bytes = (m_max * n_total * 2 + 255) // 256 * 256
+        total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word
+        ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        _lib.check(self.lib.b200q_ipc_alloc(total, ctypes.byref(ptr), handle))
+        self._own = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.base = []
+        for q in range(self.world):
+            if q == self.rank:
+                self.base.append(self._own)
+            else:
+                p = ctypes.c_void_p()
+                h = (ctypes.c_ubyte * 64).from_buffer_copy(handles[q])
+                _lib.check(self.lib.b200q_ipc_open(h, ctypes.byref(p)))
+                self.base.append(p.value)
+        self.flag = [b + self.N_BUF * self.buf_bytes for b in self.base]
+        self.step = 0
+        dist.barrier(group=group)   # nobody stores into a buffer that is not mapped yet
+
+    def y_ptrs(self, buf: int):
+        return (ctypes.c_void_p * self.world)(*[b + buf * self.buf_bytes for b in self.base])
+
+    def flag_ptrs(self):
+        return (ctypes.c_void_p * self.world)(*self.flag)
+
+    def local(self, buf: int, m: int) -> torch.Tensor:
+        """This rank's copy of the gathered [m, n_total] result in buffer `buf`."""
+        t = torch.as_tensor(_DevMem(self._own + buf * self.buf_bytes, self.m_max * self.n_total), device="cuda")
+        return t.view(torch.bfloat16).view(self.m_max, self.n_total)[:m]
+
+    def close(self):
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)   # no rank may still be storing into a buffer that goes away
+        for q, b in enumerate(self.base):
+            if q != self.rank:
+                self.lib.b200q_ipc_close(ctypes.c_void_p(b))
+        self.lib.b200q_ipc_free(ctypes.c_void_p(self._own))
+        self._own = None
+
+
+def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tensor, out: PeerOutput) -> torch.Tensor:
+    """y = x @ dequant(W)^T for the full W, every rank holding only its rows: one matmul launch
+    whose epilogue stores to all ranks, one flag update, one bounded wait.  x: [M, K] bf16 CUDA,
+    the same on every rank.  Returns this rank's [M, N] view (valid until the buffer is used again
+    two calls later)."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
+        raise ValueError("[sharded_matmul_allgather] x must be a 2-D bfloat16 CUDA tensor")
+    M, K = x.shape
+    if M > out.m_max or layer.n_local * out.world != out.n_total:
+        raise ValueError("[sharded_matmul_allgather] output buffers do not match the layer")
+    lib = out.lib
+    x = x.contiguous()
+    dt = _lib.BF16
+    need = max(int(lib.b200q_qmm_workspace_bytes(dt, 1, M, layer.n_local, K, layer.group_size, layer.bits, 1)), 256)
+    ws = ops._workspaces.get(x.device, need, "qmm")
+    st = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    buf = out.step % out.N_BUF
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.check(lib.b200q_qmm_sharded(vp(x), vp(layer.weight), vp(layer.scales), vp(layer.biases), out.y_ptrs(buf),
+                                     out.world, out.n_total, out.rank * layer.n_local, dt, M, layer.n_local, K,
+                                     layer.group_size, layer.bits, vp(ws), ws.numel(), st))
+    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, st))
+    out.step += 1
+    status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
+    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), out.step * out.world, status, st))
+    return out.local(buf, M)

@@ -1,0 +1,49 @@
+"""Worker of tests/test_peer_gpu.py: one process per GPU (launched with torch.distributed.run).
+Checks the matmul with the all_gather fused into its epilogue against the oracle on every rank."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import mlx_b200 as mb  # noqa: E402
+import oracle as O  # noqa: E402
+from mlx_b200 import _lib, ops  # noqa: E402
+from mlx_b200.distributed import PeerOutput, QuantizedAllToShardedLinear, sharded_matmul_allgather  # noqa: E402
+from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("gloo")   # plumbing only: exchanges the 64-byte IPC handles
+    N, K, g = 1024, 512, 64
+    wq, s, b = O.quantize(make_w(5, (N, K), "bf16"), g, 4, "bf16")
+    layer = QuantizedAllToShardedLinear(u32_to_torch(wq), to_torch(s, "bf16"), to_torch(b, "bf16"), g, 4,
+                                        rank=rank, world=world)
+    out = PeerOutput(96, N)
+    ok = True
+    for step, M in enumerate((16, 1, 96, 7, 16)):   # decode kernel (M <= 16) and tensor-core kernel
+        x = make_x(20 + step, (M, K), "bf16")
+        y = sharded_matmul_allgather(layer, to_torch(x, "bf16"), out)
+        torch.cuda.synchronize()
+        ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
+        good, rel = qmm_close(O.to_f32(from_torch(y.contiguous()), "bf16"), ref)
+        st = (__import__("ctypes").c_uint32 * 4)()
+        ws = ops._workspaces.get(y.device, 0, "qmm")
+        _lib.load().b200q_read_status(__import__("ctypes").c_void_p(ws.data_ptr()), ws.numel(), None, st)
+        print(f"rank {rank} step {step} M={M} ok={good} rel={rel:.4f} status={st[0]}", flush=True)
+        ok = ok and good and st[0] == 0
+        dist.barrier()
+    out.close()
+    dist.destroy_process_group()
+    print(f"rank {rank} {'PEER-OK' if ok else 'PEER-FAIL'}", flush=True)
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
