@@ -176,6 +176,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200q")
+    ap.add_argument("--gather", default="fused", choices=("fused", "nccl"),
+                    help="N > 1: all_gather fused into the matmul epilogue (peer stores) or the NCCL collective")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -225,7 +227,18 @@ def main():
     class Gather:  # cache holder for the all_gather staging buffer
         _gather_buf = None
 
+    # N > 1: by default the all_gather is fused into the matmul epilogue (peer stores into every
+    # rank's output buffer, flag signal + bounded wait); --gather nccl runs the collective instead.
+    fused = world > 1 and args.gather == "fused"
+    if fused:
+        from mlx_b200.distributed import PeerOutput, QuantizedAllToShardedLinear, sharded_matmul_allgather
+        peer_out = PeerOutput(M_DEC, N_DEC)
+        layers = [QuantizedAllToShardedLinear(q, s, b, GROUP, BITS, rank=rank, world=world, already_sharded=True)
+                  for (q, s, b) in weights]
+
     def step(i):
+        if fused:
+            return sharded_matmul_allgather(layers[i % WEIGHT_COPIES], x, peer_out)
         q, s, b = weights[i % WEIGHT_COPIES]
         rc = lib.b200q_qmm(P(x), P(q), P(s), P(b), P(y), _lib.BF16, 1, M_DEC, n_loc, K_DEC, GROUP, BITS, 1, 0,
                            P(ws), ws.numel(), sp)
@@ -245,12 +258,12 @@ def main():
             step(i)
     barrier()
 
-    # ---- device-timed region: exactly `steps` steps on the launching stream.  At one GPU the
-    # steps are replayed from a CUDA graph (no host launch gaps); with NCCL they run eagerly.
+    # ---- device-timed region: exactly `steps` steps on the launching stream, replayed from a CUDA
+    # graph (no host launch gaps); with the NCCL collective in the step they run eagerly.
     sampler = ClockSampler(local_rank)
     launches0 = lib.b200q_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if world == 1:
+    if world == 1 or fused:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i in range(args.steps):
@@ -384,17 +397,19 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"decode quantized_matmul M={M_DEC} N={N_DEC} K={K_DEC} bits={BITS} group={GROUP} "
                                    "transpose=True (Llama-3-8B MLP up-projection), N-sharded over the ranks"
-                                   + (", all_gather of outputs per step" if world > 1 else ""),
+                                   + ((", all_gather of outputs per step " + ("fused into the kernel epilogue (peer stores over NVLink)" if fused else "by NCCL")) if world > 1 else ""),
                        "l2": f"weights rotated over {WEIGHT_COPIES} distinct copies "
                              f"({WEIGHT_COPIES * algorithmic_bytes(0, n_loc, K_DEC) / 1e6:.0f} MB per rank) so reads "
                              "come from HBM",
-                       "timing": "CUDA events on the launching stream" + (", steps replayed from one CUDA graph" if world == 1 else ""),
+                       "timing": "CUDA events on the launching stream" + (", steps replayed from one CUDA graph" if (world == 1 or fused) else ""),
                        "parallelism": f"n-shard x{world}"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "prefill": prefill,
             "cpu_baseline": cpu_baseline, "device_status": list(status), "e2e_matches_device": ok_check,
         }
         print(json.dumps(line))
     if world > 1:
+        if fused:
+            peer_out.close()
         dist.destroy_process_group()
 
 

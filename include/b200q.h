@@ -177,19 +177,22 @@ int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const void* scale
  * full output), col0 = rank * N_local.  bfloat16, transpose form only; other problems
  * return B200Q_ERR_UNSUPPORTED (use b200q_qmm and a collective).
  *
- * Completion across ranks uses one 32-bit flag word per rank that only ever grows:
- * after b200q_qmm_sharded, b200q_peer_signal adds 1 to the flag of every rank (system
- * scope, ordered after all earlier work on `stream`); b200q_peer_wait makes `stream`
- * wait until the local flag has reached `expected` (= step * world size).  The wait is
- * bounded (about one second): when it runs out, code 6 is stored in status[0] (device
- * memory, 4 words, e.g. the status word of the workspace) and the stream continues.
+ * Completion across ranks uses two 32-bit words per rank that only ever grow: a flag that
+ * every rank adds 1 to once per step, and a local epoch.  After b200q_qmm_sharded,
+ * b200q_peer_signal (ordered after all earlier work on `stream`, system scope) adds
+ * n_peers to the local epoch and 1 to the flag of every rank; b200q_peer_wait makes
+ * `stream` wait until the local flag has reached the local epoch, i.e. until every
+ * rank's block of this step has landed.  Both values live on the device, so a captured
+ * sequence can be replayed.  The wait is bounded (about one second): when it runs out,
+ * code 6 is stored in status[0] (device memory, 4 words, e.g. the status word of the
+ * workspace) and the stream continues.  Flag and epoch must start at zero.
  */
 int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                       void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
                       int64_t M, int64_t N_local, int64_t K, int group_size, int bits, void* ws,
                       size_t ws_bytes, void* stream);
-int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, void* stream);
-int b200q_peer_wait(const uint32_t* flag_local, uint32_t expected, uint32_t* status, void* stream);
+int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_local, void* stream);
+int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream);
 
 /*
  * Set-up helpers for the peer buffers (not capture-safe, they allocate): a buffer that

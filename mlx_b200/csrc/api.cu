@@ -177,14 +177,16 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
 namespace b200q {
 namespace peer {
 __global__ void peer_signal_kernel(uint32_t* f0, uint32_t* f1, uint32_t* f2, uint32_t* f3, uint32_t* f4, uint32_t* f5,
-                                   uint32_t* f6, uint32_t* f7, int n) {
+                                   uint32_t* f6, uint32_t* f7, int n, uint32_t* epoch) {
   uint32_t* f[kMaxPeers] = {f0, f1, f2, f3, f4, f5, f6, f7};
   // everything enqueued before this kernel on the stream (the peer stores of the matmul) has
   // completed; the fence orders it before the flag updates for observers on other GPUs
   __threadfence_system();
+  *epoch += (uint32_t)n;   // what the local flag must reach before this step's output is complete
   for (int q = 0; q < n; ++q) atomicAdd_system(f[q], 1u);
 }
-__global__ void peer_wait_kernel(const uint32_t* flag, uint32_t expected, uint32_t* status) {
+__global__ void peer_wait_kernel(const uint32_t* flag, const uint32_t* epoch, uint32_t* status) {
+  const uint32_t expected = *epoch;
   const long long t0 = clock64();
   const long long limit = 2000000000ll;  // about one second of SM clocks
   for (;;) {
@@ -226,22 +228,22 @@ extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* 
   return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
 }
 
-extern "C" int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, void* stream) {
-  if (!flag_peers || n_peers < 1 || n_peers > kMaxPeers)
+extern "C" int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_local, void* stream) {
+  if (!flag_peers || !epoch_local || n_peers < 1 || n_peers > kMaxPeers)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_signal] between 1 and %d flags are supported (got %d)", kMaxPeers, n_peers);
   uint32_t* f[kMaxPeers] = {};
   for (int q = 0; q < n_peers; ++q) {
     if (!flag_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_signal] null flag %d", q);
     f[q] = flag_peers[q];
   }
-  peer::peer_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], n_peers);
+  peer::peer_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], n_peers, epoch_local);
   B200Q_LAUNCH_OK("peer_signal_kernel");
   return B200Q_OK;
 }
 
-extern "C" int b200q_peer_wait(const uint32_t* flag_local, uint32_t expected, uint32_t* status, void* stream) {
-  if (!flag_local || !status) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_wait] null pointer");
-  peer::peer_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag_local, expected, status);
+extern "C" int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream) {
+  if (!flag_local || !epoch_local || !status) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_wait] null pointer");
+  peer::peer_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag_local, epoch_local, status);
   B200Q_LAUNCH_OK("peer_wait_kernel");
   return B200Q_OK;
 }

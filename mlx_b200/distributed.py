@@ -132,7 +132,7 @@ class PeerOutput:
             raise ValueError("at most 8 ranks can share output buffers")
         self.m_max, self.n_total = m_max, n_total
         self.buf_bytes = (m_max * n_total * 2 + 255) // 256 * 256
-        total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word
+        total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word and (at +128) the epoch
         ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
         _lib.check(self.lib.b200q_ipc_alloc(total, ctypes.byref(ptr), handle))
         self._own = ptr.value
@@ -148,7 +148,11 @@ class PeerOutput:
                 _lib.check(self.lib.b200q_ipc_open(h, ctypes.byref(p)))
                 self.base.append(p.value)
         self.flag = [b + self.N_BUF * self.buf_bytes for b in self.base]
+        self.epoch = self._own + self.N_BUF * self.buf_bytes + 128
         self.step = 0
+        # torch views of the local buffers, made once (nothing is created during stream capture)
+        self._views = [torch.as_tensor(_DevMem(self._own + i * self.buf_bytes, m_max * n_total), device="cuda")
+                       .view(torch.bfloat16).view(m_max, n_total) for i in range(self.N_BUF)]
         dist.barrier(group=group)   # nobody stores into a buffer that is not mapped yet
 
     def y_ptrs(self, buf: int):
@@ -159,8 +163,7 @@ class PeerOutput:
 
     def local(self, buf: int, m: int) -> torch.Tensor:
         """This rank's copy of the gathered [m, n_total] result in buffer `buf`."""
-        t = torch.as_tensor(_DevMem(self._own + buf * self.buf_bytes, self.m_max * self.n_total), device="cuda")
-        return t.view(torch.bfloat16).view(self.m_max, self.n_total)[:m]
+        return self._views[buf][:m]
 
     def close(self):
         if self._own is None:
@@ -195,8 +198,8 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
     _lib.check(lib.b200q_qmm_sharded(vp(x), vp(layer.weight), vp(layer.scales), vp(layer.biases), out.y_ptrs(buf),
                                      out.world, out.n_total, out.rank * layer.n_local, dt, M, layer.n_local, K,
                                      layer.group_size, layer.bits, vp(ws), ws.numel(), st))
-    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, st))
+    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, ctypes.c_void_p(out.epoch), st))
     out.step += 1
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
-    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), out.step * out.world, status, st))
+    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     return out.local(buf, M)
