@@ -71,3 +71,20 @@ def test_kernel_selection_names():
     assert name(16, 4096, 4096, tr=0) == "qmm_generic"
     assert name(4, 100, 96, g=32) == "qmm_generic"
     assert lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, 16, 14336, 4096, 64, 4, 1) > 14336 * 64
+
+
+def test_sharded_rejects_on_host():
+    """b200q_qmm_sharded validates its output description before any CUDA call."""
+    lib = _lib.load()
+    dummy = ctypes.c_void_p(4096)
+    one = (ctypes.c_void_p * 1)(4096)
+    nine = (ctypes.c_void_p * 9)(*([4096] * 9))
+    call = lambda ys, n, ld, col0, nl=128: lib.b200q_qmm_sharded(dummy, dummy, dummy, dummy, ys, n, ld, col0, _lib.BF16, 4, nl,
+                                                                  256, 64, 4, dummy, 1 << 20, None)
+    assert call(one, 0, 256, 0) == _lib.ERR_INVALID_ARGUMENT           # no output buffer
+    assert call(nine, 9, 256, 0) == _lib.ERR_INVALID_ARGUMENT          # more than 8 ranks
+    assert call(one, 1, 64, 0) == _lib.ERR_INVALID_ARGUMENT            # row pitch below the local width
+    assert call(one, 1, 256, 192) == _lib.ERR_INVALID_ARGUMENT         # columns [192, 320) outside a pitch of 256
+    assert b"fit a row pitch" in lib.b200q_last_error()
+    assert lib.b200q_peer_signal(None, 2, dummy, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.b200q_peer_wait(None, dummy, dummy, None) == _lib.ERR_INVALID_ARGUMENT
