@@ -88,12 +88,30 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ wq, T* __restric
 
   uint64_t packed = 0;
   if (active) {
+    // q = rint((w - bias) / scale) with the IEEE division of the reference, but the division is
+    // only carried out where it can matter: t = (w - bias) * (1 / scale) is within 1.2e-7 * |t|
+    // of the true quotient, so rint(t) equals rint of the rounded quotient unless t lies within
+    // that distance of a rounding tie k + 1/2.  Below |t| = 512 that is less than 1e-4; above, both
+    // roundings clamp to the same bin.  Threads that see a t closer than 1e-4 to a tie (or a NaN)
+    // redo their eight values with the exact division.
+    const float inv = __frcp_rn(scale);
+    float q[8];
+    bool redo = !(fabsf(scale) < 1e30f);   // 1/scale would lose bits as a subnormal
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float q = rintf(__fdiv_rn(__fsub_rn(v[i], bias), scale));
-      q = (q < 0.0f) ? 0.0f : q;
-      q = (n_bins < q) ? n_bins : q;
-      packed |= (uint64_t)(uint32_t)q << (i * BITS);
+      const float t = __fmul_rn(__fsub_rn(v[i], bias), inv);
+      q[i] = rintf(t);
+      redo |= !(fabsf(fabsf(__fsub_rn(t, q[i])) - 0.5f) >= 1e-4f);   // also true for NaN
+    }
+    if (redo) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = rintf(__fdiv_rn(__fsub_rn(v[i], bias), scale));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float qi = (q[i] < 0.0f) ? 0.0f : q[i];
+      qi = (n_bins < qi) ? n_bins : qi;
+      packed |= (uint64_t)(uint32_t)qi << (i * BITS);
     }
     if ((c % LPG) == 0) {
       scales[c / LPG] = Elem<T>::from_float(scale);
@@ -101,6 +119,14 @@ quantize_kernel(const T* __restrict__ w, uint32_t* __restrict__ wq, T* __restric
     }
   }
 
+  // 4 and 8 bits: a thread's eight fields are exactly one or two words.
+  if constexpr (BITS == 4) {
+    if (active) wq[c] = (uint32_t)packed;
+    return;
+  } else if constexpr (BITS == 8) {
+    if (active) reinterpret_cast<uint2*>(wq)[c] = make_uint2((uint32_t)packed, (uint32_t)(packed >> 32));
+    return;
+  }
   // Merge the four 8*BITS-bit fragments of a quad into BITS whole words.
   constexpr int SEG = 8 * BITS;
   const int qbase = lane & ~3;

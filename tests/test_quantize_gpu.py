@@ -98,3 +98,28 @@ def test_round_trip_large_matrix_properties():
         ref = O.quantize(from_torch(w[rows]), g, bits, "bf16")
         wq_rows = wq.view(torch.int32)[rows].view(torch.uint32)  # torch cannot index uint32 directly
         assert same(ref[0], from_torch(wq_rows)) and same(ref[1], from_torch(s[rows])) and same(ref[2], from_torch(b[rows]))
+
+
+@pytest.mark.parametrize("dtype", ("f32", "bf16", "f16"))
+@pytest.mark.parametrize("g,bits", [(32, 2), (64, 3), (64, 4), (128, 5), (32, 6), (128, 8)])
+def test_quantize_rounding_ties_and_extremes(dtype, g, bits):
+    """The kernel replaces most divisions by a multiplication with 1/scale and redoes the exact
+    division only near rounding ties: inputs that sit ON the ties (k + 1/2 steps of the grid),
+    huge and tiny magnitudes and groups with zeros must still be bit-exact."""
+    rng = np.random.default_rng(bits * 100 + g)
+    rows, K = 48, 1024
+    nb = (1 << bits) - 1
+    base = rng.standard_normal((rows, K)).astype(np.float32)
+    grid = rng.integers(0, 2 * nb + 1, size=(rows, K)).astype(np.float32) * 0.5   # 0, 0.5, ..., nb
+    grid[:, ::g] = 0.0
+    grid[:, 1::g] = nb
+    zeros = base.copy()
+    zeros[::7, ::5] = 0.0
+    cases = [grid, -grid, grid * 0.125 + 3.0, base * (1e30 if dtype != "f16" else 1e3),
+             base * (1e-30 if dtype == "f32" else 1e-6), zeros]
+    for ci, w in enumerate(cases):
+        wd = O.to_dtype(w, dtype)
+        rq, rs, rb = O.quantize(wd, g, bits, dtype)
+        q, s, b = mb.quantize(to_torch(wd, dtype), g, bits)
+        assert np.array_equal(from_torch(q).view(np.uint32), rq.view(np.uint32)), (ci, "wq")
+        assert np.array_equal(from_torch(s), rs) and np.array_equal(from_torch(b), rb), (ci, "scales/biases")
