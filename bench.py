@@ -39,9 +39,10 @@ METRIC = "4-bit g64 qmm: decode GB/s & prefill TFLOPS at 1/2/4/8 B200 vs rooflin
 M_DEC, N_DEC, K_DEC, GROUP, BITS = 16, 14336, 4096, 64, 4
 M_PRE = 4096
 WEIGHT_COPIES = 8
-# dram__bytes_read+write per launch of the decode kernel from the ncu capture summarised in
-# profiles/ (None until a capture of the current kernel exists)
-NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of qmv_mma_kernel on the one-GPU decode
+# workload (profiles/qmv_mma_kernel_decode_M16_N14336_K4096.md); with the matrix split over R
+# ranks the per-rank traffic is this divided by R (it is all weight stream)
+NCU_TRAFFIC_BYTES = 33494784
 
 
 def algorithmic_bytes(M, N, K, bits=BITS, group=GROUP):
@@ -318,7 +319,7 @@ def main():
     hbm_peak, tf_peak, peak_src = measured_peaks()
     achieved = algorithmic_bytes(M_DEC, n_loc, K_DEC) / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "traffic": NCU_TRAFFIC_BYTES, "kernel": kernel, "kernel_us": kernel_ms * 1e3, "peak_source": peak_src}
+                "traffic": (NCU_TRAFFIC_BYTES // world if kernel == "qmv_mma" else None), "kernel": kernel, "kernel_us": kernel_ms * 1e3, "peak_source": peak_src}
 
     # ---- end to end through the host-buffer C-ABI call (pinned host x and y, copies timed)
     x_host = torch.empty(M_DEC, K_DEC, dtype=torch.bfloat16).pin_memory()
