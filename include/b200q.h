@@ -191,6 +191,25 @@ int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* scales, con
                       void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
                       int64_t M, int64_t N_local, int64_t K, int group_size, int bits, void* ws,
                       size_t ws_bytes, void* stream);
+/*
+ * Expert-parallel gather_qmm: the E_total weight matrices are spread over the ranks in
+ * contiguous blocks (this rank holds experts [e_lo, e_lo + E_local) in wq_local /
+ * scales_local / biases_local), x and the index pairs are the same on every rank.  Every
+ * rank multiplies only the pairs of its own experts and stores each result row into the
+ * [n_idx * M, N] output buffer of EVERY rank (y_peers, self = index of this rank's own
+ * buffer), so after b200q_peer_signal / b200q_peer_wait all ranks hold the complete
+ * output: a variable-size all_gather without padding or a collective.  Replaces
+ * GatherQMM::eval_gpu (mlx/backend/cuda/quantized/quantized.cpp:154-278) followed by the
+ * exchange of the rows in an expert-parallel layer.  bfloat16, transpose form, K a multiple
+ * of 128 only (B200Q_ERR_UNSUPPORTED otherwise).  Workspace as b200q_gather_qmm with E =
+ * E_total.  Out-of-range indices: as b200q_gather_qmm, zeroed in this rank's own buffer.
+ */
+int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local, const void* scales_local,
+                             const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
+                             int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
+                             int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                             int64_t N, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
+                             void* stream);
 int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_local, void* stream);
 int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream);
 

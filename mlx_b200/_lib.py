@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200q_qmm_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i, _i, _i, _vp, _sz, _vp]),
     "b200q_qmm_decode_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i, _i, _vp]),
     "b200q_qmm_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i64, _i64, _i64, _i, _i, _vp, _sz, _vp]),
+    "b200q_gather_qmm_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
+                                      _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_peer_signal": (_i, [_vp, _i, _vp, _vp]),
     "b200q_peer_wait": (_i, [_vp, _vp, _vp, _vp]),
     "b200q_ipc_alloc": (_i, [_sz, _vp, _vp]),

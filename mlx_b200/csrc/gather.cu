@@ -28,17 +28,19 @@ constexpr int kMaxExpertsFast = 1024;
 
 __global__ void __launch_bounds__(1024)
 gather_sort_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict__ rhs, int n_idx, uint32_t x_batch,
-                   uint32_t E, int M, int NT, Header* hdr, int* __restrict__ sorted_slot, MTileRec* __restrict__ mtiles,
+                   uint32_t E_total, uint32_t e_lo, uint32_t E, int M, int NT, Header* hdr, int* __restrict__ sorted_slot, MTileRec* __restrict__ mtiles,
                    void* y, size_t y_slot_bytes, uint32_t* status) {
   __shared__ int counts[kMaxExpertsFast];
   __shared__ int cursor[kMaxExpertsFast];
   const int tid = threadIdx.x;
   for (int e = tid; e < (int)E; e += blockDim.x) counts[e] = 0;
   __syncthreads();
+  // Experts [e_lo, e_lo + E) are the ones whose weights this call holds (all of them unless the
+  // experts are spread over several GPUs); pairs for other valid experts are somebody else's.
   for (int i = tid; i < n_idx; i += blockDim.x) {
     const uint32_t e = rhs[i], l = lhs[i];
-    if (e < E && l < x_batch) {
-      atomicAdd(&counts[e], 1);
+    if (e < E_total && l < x_batch) {
+      if (e - e_lo < E) atomicAdd(&counts[e - e_lo], 1);
     } else {
       // out-of-range index: record it; its output rows are zeroed below, nothing is read through it
       atomicMax(&status[0], 1u);
@@ -66,8 +68,8 @@ gather_sort_kernel(const uint32_t* __restrict__ lhs, const uint32_t* __restrict_
   __syncthreads();
   for (int i = tid; i < n_idx; i += blockDim.x) {
     const uint32_t e = rhs[i], l = lhs[i];
-    if (e < E && l < x_batch) {
-      sorted_slot[atomicAdd(&cursor[e], 1)] = i;
+    if (e < E_total && l < x_batch) {
+      if (e - e_lo < E) sorted_slot[atomicAdd(&cursor[e - e_lo], 1)] = i;
     } else {
       unsigned short* dst = reinterpret_cast<unsigned short*>(static_cast<char*>(y) + (size_t)i * y_slot_bytes);
       for (size_t b = 0; b < y_slot_bytes / 2; ++b) dst[b] = 0;
@@ -132,6 +134,37 @@ bool fast_supported(int dtype, int64_t n_idx, int64_t x_batch, int64_t E, int64_
   return true;
 }
 
+
+// Sort by expert, gather the activation rows, one grouped tensor-core launch.  Experts
+// [e_lo, e_lo + E_local) of E_total are the ones whose weights `wq` holds; with `peers` every
+// result row is stored into all of the given [n_idx * M, N] buffers.
+int run_grouped(const void* x, const uint32_t* wq, const void* scales, const void* biases, const uint32_t* lhs_idx,
+                const uint32_t* rhs_idx, int64_t n_idx, void* y, const PeerOut* peers, int64_t x_batch, int64_t E_total,
+                int64_t e_lo, int64_t E_local, int64_t M, int64_t N, int64_t K, int group_size, int bits, void* ws,
+                size_t ws_bytes, cudaStream_t st) {
+  uint32_t* status = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes);
+  const FastLayout L = fast_layout(n_idx, E_total, M, K);
+  char* base = static_cast<char*>(ws);
+  Header* hdr = reinterpret_cast<Header*>(base + L.hdr);
+  int* sorted = reinterpret_cast<int*>(base + L.sorted);
+  int* dst = reinterpret_cast<int*>(base + L.dst);
+  MTileRec* mt = reinterpret_cast<MTileRec*>(base + L.mtiles);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + L.xs);
+  gather_sort_kernel<<<1, 1024, 0, st>>>(lhs_idx, rhs_idx, (int)n_idx, (uint32_t)x_batch, (uint32_t)E_total, (uint32_t)e_lo,
+                                         (uint32_t)E_local, (int)M, L.nt, hdr, sorted, mt, y, (size_t)M * N * 2, status);
+  B200Q_LAUNCH_OK("gather_sort_kernel");
+  gather_rows_kernel<<<(unsigned)L.n_rows, 256, 0, st>>>((const __nv_bfloat16*)x, lhs_idx, hdr, sorted, (int)M, (int)K,
+                                                         xs, dst);
+  B200Q_LAUNCH_OK("gather_rows_kernel");
+  GroupedArgs g{};
+  g.x_sorted = xs; g.wq = wq; g.scales = scales; g.biases = biases; g.y = y;
+  g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles; g.dst_row = dst;
+  g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E_local; g.N = N; g.K = K;
+  g.group = group_size; g.bits = bits; g.nt = L.nt; g.status = status;
+  if (peers) g.peers = *peers;
+  return qmm_tc_grouped(g, st);
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -181,27 +214,9 @@ extern "C" int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* s
 
   const bool aligned = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wq) |
                           reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(y)) & 15);
-  if (aligned && fast_supported(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose)) {
-    const FastLayout L = fast_layout(n_idx, E, M, K);
-    char* base = static_cast<char*>(ws);
-    Header* hdr = reinterpret_cast<Header*>(base + L.hdr);
-    int* sorted = reinterpret_cast<int*>(base + L.sorted);
-    int* dst = reinterpret_cast<int*>(base + L.dst);
-    MTileRec* mt = reinterpret_cast<MTileRec*>(base + L.mtiles);
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + L.xs);
-    gather_sort_kernel<<<1, 1024, 0, st>>>(lhs_idx, rhs_idx, (int)n_idx, (uint32_t)x_batch, (uint32_t)E, (int)M, L.nt,
-                                           hdr, sorted, mt, y, (size_t)M * N * 2, status);
-    B200Q_LAUNCH_OK("gather_sort_kernel");
-    gather_rows_kernel<<<(unsigned)L.n_rows, 256, 0, st>>>((const __nv_bfloat16*)x, lhs_idx, hdr, sorted, (int)M, (int)K,
-                                                           xs, dst);
-    B200Q_LAUNCH_OK("gather_rows_kernel");
-    GroupedArgs g{};
-    g.x_sorted = xs; g.wq = wq; g.scales = scales; g.biases = biases; g.y = y;
-    g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles; g.dst_row = dst;
-    g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E; g.N = N; g.K = K;
-    g.group = group_size; g.bits = bits; g.nt = L.nt; g.status = status;
-    return qmm_tc_grouped(g, st);
-  }
+  if (aligned && fast_supported(dtype, n_idx, x_batch, E, M, N, K, group_size, bits, transpose))
+    return run_grouped(x, wq, scales, biases, lhs_idx, rhs_idx, n_idx, y, nullptr, x_batch, E, 0, E, M, N, K, group_size,
+                       bits, ws, ws_bytes, st);
 
   QmmArgs a{};
   a.x = x; a.wq = wq; a.scales = scales; a.biases = biases; a.y = y;
@@ -210,4 +225,40 @@ extern "C" int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* s
   a.ws = ws; a.ws_bytes = ws_bytes;
   GatherIdx gi{lhs_idx, rhs_idx, (uint32_t)x_batch, (uint32_t)E, status};
   return qmm_generic(a, st, &gi);
+}
+
+extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local, const void* scales_local,
+                                        const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
+                                        int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
+                                        int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                                        int64_t N, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
+                                        void* stream) {
+  if (!y_peers || n_peers < 1 || n_peers > kMaxPeers || self < 0 || self >= n_peers)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] between 1 and %d output buffers, one of them this rank's (got %d, self %d)",
+                kMaxPeers, n_peers, self);
+  if (!valid_group(group_size) || !valid_bits(bits))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] group size must be 32, 64 or 128 and bits 2, 3, 4, 5, 6 or 8");
+  if (n_idx < 0 || x_batch < 0 || M < 0 || N < 0 || K < 0 || E_total < 1 || e_lo < 0 || E_local < 0 || e_lo + E_local > E_total)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] experts [%lld, %lld) are not a range of %lld experts",
+                (long long)e_lo, (long long)(e_lo + E_local), (long long)E_total);
+  if (K % group_size != 0 || (K * bits) % 32 != 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] The shapes of the weight and scales are incompatible based on bits and group_size");
+  if (n_idx == 0 || M == 0 || N == 0) return B200Q_OK;
+  PeerOut peers{};
+  for (int q = 0; q < n_peers; ++q) {
+    if (!y_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null output buffer %d", q);
+    peers.y[q] = y_peers[q];
+  }
+  peers.n = n_peers; peers.ld = N; peers.col0 = 0;
+  if (!x || !wq_local || !scales_local || !biases_local || !lhs_idx || !rhs_idx)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null pointer");
+  const size_t need = b200q_gather_qmm_workspace_bytes(dtype, n_idx, x_batch, E_total, M, N, K, group_size, bits, 1);
+  if (!ws || ws_bytes < need)
+    return fail(B200Q_ERR_WORKSPACE, "[gather_qmm_sharded] workspace of %zu bytes required, %zu given", need, ws_bytes);
+  const bool aligned = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wq_local) |
+                          reinterpret_cast<uintptr_t>(ws)) & 15);
+  if (!aligned || E_local < 1 || !fast_supported(dtype, n_idx, x_batch, E_total, M, N, K, group_size, bits, 1))
+    return fail(B200Q_ERR_UNSUPPORTED, "[gather_qmm_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
+  return run_grouped(x, wq_local, scales_local, biases_local, lhs_idx, rhs_idx, n_idx, y_peers[self], &peers, x_batch, E_total,
+                     e_lo, E_local, M, N, K, group_size, bits, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }

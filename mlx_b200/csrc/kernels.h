@@ -49,6 +49,7 @@ struct GroupedArgs {
   int64_t n_rows, max_mtiles, E, N, K;
   int group, bits, nt;
   uint32_t* status;
+  PeerOut peers;            // n > 0: every result row is stored into all of these [n_rows, N] buffers
 };
 
 // Per-problem operand selection of the gather form: problem i of `batch` multiplies

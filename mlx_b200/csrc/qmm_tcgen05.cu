@@ -442,9 +442,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             }
           } else {
             const int* dr = p.dst_row + m0 + c;
+            for (int q = 0; q < p.n_out; ++q) {
+              __nv_bfloat16* yq = p.y_out[q] + n;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < lim) p.y[(size_t)dr[j] * p.N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              for (int j = 0; j < 32; ++j)
+                if (j < lim) yq[(size_t)dr[j] * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
           }
         }
       }
@@ -611,6 +614,13 @@ int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
   p.scales = (const __nv_bfloat16*)a.scales;
   p.biases = (const __nv_bfloat16*)a.biases;
   p.y = (__nv_bfloat16*)a.y;
+  if (a.peers.n > 0) {
+    p.n_out = a.peers.n;
+    for (int q = 0; q < a.peers.n; ++q) p.y_out[q] = (__nv_bfloat16*)a.peers.y[q];
+  } else {
+    p.n_out = 1; p.y_out[0] = (__nv_bfloat16*)a.y;
+  }
+  p.ld = a.N; p.col0 = 0;
   p.status = a.status;
   p.M = (int)a.n_rows; p.N = (int)a.N; p.K = (int)a.K;
   p.NT = nt;

@@ -203,3 +203,37 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
     _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     return out.local(buf, M)
+
+
+def sharded_gather_qmm(x: torch.Tensor, w_local: torch.Tensor, scales_local: torch.Tensor, biases_local: torch.Tensor,
+                       lhs_indices: torch.Tensor, rhs_indices: torch.Tensor, e_lo: int, n_experts: int,
+                       out: PeerOutput, group_size: int = 64, bits: int = 4) -> torch.Tensor:
+    """Expert-parallel gather_qmm: this rank holds experts [e_lo, e_lo + E_local) of `n_experts`
+    (`expert_bounds`), x [B, M, K] bf16 and the flat index pairs are the same on every rank.  Every
+    rank multiplies the pairs of its own experts and stores the rows into every rank's buffer;
+    returns this rank's complete [n_idx, M, N] (valid until the buffer is used again two calls later)."""
+    if x.dtype != torch.bfloat16 or x.dim() != 3 or not x.is_cuda:
+        raise ValueError("[sharded_gather_qmm] x must be a [B, M, K] bfloat16 CUDA tensor")
+    B, M, K = x.shape
+    E_local, N = w_local.shape[0], w_local.shape[1]
+    lhs32 = lhs_indices.reshape(-1).to(device=x.device, dtype=torch.int32).contiguous()
+    rhs32 = rhs_indices.reshape(-1).to(device=x.device, dtype=torch.int32).contiguous()
+    n_idx = rhs32.numel()
+    if lhs32.numel() != n_idx or n_idx * M > out.m_max or N != out.n_total:
+        raise ValueError("[sharded_gather_qmm] index arrays / output buffers do not match the problem")
+    lib = out.lib
+    x = x.contiguous()
+    dt = _lib.BF16
+    need = max(int(lib.b200q_gather_qmm_workspace_bytes(dt, n_idx, B, n_experts, M, N, K, group_size, bits, 1)), 256)
+    ws = ops._workspaces.get(x.device, need, "gather")
+    st = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    buf = out.step % out.N_BUF
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.check(lib.b200q_gather_qmm_sharded(vp(x), vp(w_local), vp(scales_local), vp(biases_local), vp(lhs32), vp(rhs32),
+                                            n_idx, out.y_ptrs(buf), out.world, out.rank, dt, B, n_experts, e_lo, E_local,
+                                            M, N, K, group_size, bits, vp(ws), ws.numel(), st))
+    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, ctypes.c_void_p(out.epoch), st))
+    out.step += 1
+    status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
+    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
+    return out.local(buf, n_idx * M).view(n_idx, M, N)

@@ -13,7 +13,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 import mlx_b200 as mb  # noqa: E402
 import oracle as O  # noqa: E402
 from mlx_b200 import _lib, ops  # noqa: E402
-from mlx_b200.distributed import PeerOutput, QuantizedAllToShardedLinear, sharded_matmul_allgather  # noqa: E402
+from mlx_b200.distributed import (PeerOutput, QuantizedAllToShardedLinear, expert_bounds, sharded_gather_qmm,  # noqa: E402
+                                  sharded_matmul_allgather)
 from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch  # noqa: E402
 
 
@@ -40,6 +41,28 @@ def main():
         ok = ok and good and st[0] == 0
         dist.barrier()
     out.close()
+
+    # ---- expert-parallel gather_qmm: 8 experts over the ranks, 40 tokens, top-2
+    E, tokens, topk, N2, K2 = 8, 40, 2, 256, 512
+    wq2, s2, b2 = O.quantize(make_w(7, (E, N2, K2), "bf16"), g, 4, "bf16")
+    x2 = make_x(8, (tokens, 1, K2), "bf16")
+    rng = np.random.default_rng(3)
+    rhs = rng.permuted(np.tile(np.arange(E), (tokens, 1)), axis=1)[:, :topk].astype(np.uint32)
+    lhs = np.broadcast_to(np.arange(tokens, dtype=np.uint32)[:, None], rhs.shape).copy()
+    lo, hi = expert_bounds(E, rank, world)
+    out2 = PeerOutput(tokens * topk, N2)
+    ref2 = O.gather_qmm(O.to_f32(x2, "bf16"), wq2, O.to_f32(s2, "bf16"), O.to_f32(b2, "bf16"), lhs.ravel(), rhs.ravel(),
+                        True, g, 4, "f32")
+    for step in range(3):
+        y2 = sharded_gather_qmm(to_torch(x2, "bf16"), u32_to_torch(wq2[lo:hi]), to_torch(s2[lo:hi], "bf16"),
+                                to_torch(b2[lo:hi], "bf16"), torch.from_numpy(lhs.astype(np.int64)),
+                                torch.from_numpy(rhs.astype(np.int64)), lo, E, out2, g, 4)
+        torch.cuda.synchronize()
+        good, rel = qmm_close(O.to_f32(from_torch(y2.contiguous()), "bf16").reshape(ref2.shape), ref2)
+        print(f"rank {rank} gather step {step} ok={good} rel={rel:.4f}", flush=True)
+        ok = ok and good
+        dist.barrier()
+    out2.close()
     dist.destroy_process_group()
     print(f"rank {rank} {'PEER-OK' if ok else 'PEER-FAIL'}", flush=True)
     sys.exit(0 if ok else 1)

@@ -88,3 +88,15 @@ def test_sharded_rejects_on_host():
     assert b"fit a row pitch" in lib.b200q_last_error()
     assert lib.b200q_peer_signal(None, 2, dummy, None) == _lib.ERR_INVALID_ARGUMENT
     assert lib.b200q_peer_wait(None, dummy, dummy, None) == _lib.ERR_INVALID_ARGUMENT
+
+
+def test_gather_sharded_rejects_on_host():
+    lib = _lib.load()
+    dummy = ctypes.c_void_p(4096)
+    two = (ctypes.c_void_p * 2)(4096, 8192)
+    call = lambda n_peers, self_, e_lo, e_loc, K=256: lib.b200q_gather_qmm_sharded(
+        dummy, dummy, dummy, dummy, dummy, dummy, 8, two, n_peers, self_, _lib.BF16, 4, 8, e_lo, e_loc, 1, 128, K, 64, 4,
+        dummy, 1 << 24, None)
+    assert call(2, 2, 0, 4) == _lib.ERR_INVALID_ARGUMENT        # self outside the buffer list
+    assert call(2, 0, 6, 4) == _lib.ERR_INVALID_ARGUMENT        # experts [6, 10) of 8
+    assert call(2, 0, 0, 4, K=96) == _lib.ERR_INVALID_ARGUMENT  # K not a multiple of the group
