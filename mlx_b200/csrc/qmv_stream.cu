@@ -315,6 +315,7 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       const bool x_ok = mbar_wait_hint(smem_u32(&bars->xbar), 0, abort_flag);
       if (!x_ok && tid == 0) atomicCAS(&p.status[2], 0u, 0x40000000u);
       if (warp == 0) QS_MARK(11);
+      if (warp == 15) QS_MARK(22);
       if (warp > 0 && warp < S && warp < n_boxes) {
         const long long j = b0 + warp;
         const int rbw = (int)(j / p.kb);
@@ -337,6 +338,8 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       }
     }
     if (warp == 0) QS_MARK(12);
+    if (warp == 3) QS_MARK(20);
+    if (warp == 15) QS_MARK(21);
     compute_barrier();
     if (warp == 0) QS_MARK(0);
     // B-fragment address of this lane inside a 32-k chunk: token g (+8b), octet t
@@ -379,6 +382,8 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
       }
     }
+    if (warp == 0) QS_MARK(23);
+    if (warp == 15) QS_MARK(24);
     compute_barrier();
     if (warp == 0) QS_MARK(1);
 
