@@ -33,6 +33,8 @@
 //   [ counters: one u32 per row block | slots: kMaxCtas x 2 x 128 rows x 16 tokens fp32 ]
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_ptx.cuh"
@@ -203,7 +205,7 @@ __host__ __device__ inline Layout make_layout(int K, int stages, int toks) {
   return L;
 }
 
-template <int MT, int GROUP>
+template <int MT, int GROUP, int NG>
 __global__ void __launch_bounds__(kThreads, 1)
 qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const SParams p) {
   constexpr int TOK = 8 * MT;
@@ -291,7 +293,12 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int g = lane >> 2, t = lane & 3;
     // warps w, w+4, w+8, w+12 share an SM sub-partition: give them the same row slice and
     // different box groups, so that a sub-partition always holds warps in different phases
-    const int r = warp & 3, gq = warp >> 2;
+    // NG == 4: group = warp / 4, the warp walks all four 64-k slices of its boxes.
+    // NG == 2 (shallow rings): group = warp / 8, two warps share a row slice and take two 64-k slices each.
+    constexpr int WPG = kWarps / NG;          // warps per group
+    constexpr int CPW = NG / 1 == 4 ? 4 : 2;    // 64-k slices per warp and box
+    const int r = warp & 3, gq = warp / WPG;
+    const int c0 = NG == 4 ? 0 : ((warp >> 2) & 1) * 2;
     const int ctid = tid;
 
     // ---- stage x: one 3-D TMA box brings [M, K] bf16 in as [K/32 chunks][TOK tokens][32 k]
@@ -324,7 +331,7 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       const int pieces = p.K / 8 * TS;
       if (x_ok) {
         for (int pi = ctid; pi < pieces; pi += kWarps * 32) {
-          if (((pi >> 2) % TS) < p.M) {
+          if (((pi >> 2) & (TS - 1)) < p.M) {   // TS is a power of two
             const uint32_t a = xs_u + (uint32_t)pi * 16;
             const uint4 v = lds128(a);
             uint4 w;
@@ -493,7 +500,7 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     int cur_rb = rb_first;
     uint32_t s = (uint32_t)gq % (uint32_t)S, ph = ((uint32_t)gq / (uint32_t)S) & 1u;
     bool ok = true;
-    for (int i = gq; i < n_boxes; i += 4) {
+    for (int i = gq; i < n_boxes; i += NG) {
       while (cur_rb < rb) { deposit(cur_rb); ++cur_rb; }
       // After a failed wait the warp keeps walking its boxes without touching the ring, so that
       // the row-block bookkeeping still completes.
@@ -518,8 +525,13 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           lds_words<GPB / 2>(b_raw[q], stage + kBiasOff + sc_lane + (uint32_t)(q * 16 * GPB));
         }
         QS_PH(ph_a);
+        // The slice index must be a compile-time value (it selects registers): the loop body is
+        // instantiated once per possible first slice of a warp.
+        auto slices = [&](auto c0c) {
+        constexpr int C0 = decltype(c0c)::value;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int cc = 0; cc < CPW; ++cc) {
+          const int c = C0 + cc;
           uint32_t w[2][4];
           uint4 xf[2][MT];
           const uint32_t xa = xlane_u + (uint32_t)((kc * 8 + 2 * c) * TS) * 64;
@@ -580,13 +592,16 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
               }
           }
         }
+        };
+        if (NG == 4 || c0 == 0) slices(std::integral_constant<int, 0>{});
+        else slices(std::integral_constant<int, 2>{});
         QS_PH(ph_b);
         // ---- release the stage: everything read from it has been consumed by instructions that
         //      had to wait for it (the MMAs for the packed words, the conversions for the scales).
         //      The last of the group's four warps refills the stage with the box S places ahead.
         __syncwarp();
         int last = 0;
-        if (lane == 0) last = atom_shared_add(smem_u32(&bars->done[s]), 1u) == 3u;
+        if (lane == 0) last = atom_shared_add(smem_u32(&bars->done[s]), 1u) == (uint32_t)(WPG - 1);
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
           if (lane == 0) bars->done[s] = 0;
@@ -598,9 +613,9 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
         QS_PH(ph_c);
       }
-      s += 4;
+      s += NG;
       while (s >= (uint32_t)S) { s -= (uint32_t)S; ph ^= 1u; }
-      kc += 4;
+      kc += NG;
       while (kc >= p.kb) { kc -= p.kb; ++rb; }
     }
     if (warp == 0) { QS_MARK(3); QS_OUT(5, prof_wait); QS_OUT(6, (uint32_t)n_boxes); }
@@ -637,24 +652,32 @@ EncodeFn encode_fn() {
 }
 
 int stored_tokens(int64_t M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : 16))); }
+// Ring depth: a multiple of the number of box groups, so that a stage is always consumed by the
+// same group (no warp can then be two barrier phases away from the one it waits for).  Eight or
+// more stages: four groups; a ring of four to seven stages runs two groups on four or six stages,
+// which leaves two or four boxes in flight while two are being worked on.
 template <int MT, int GROUP>
-int pick_stages(int K, int toks) {
-  // A multiple of the number of box groups (4): a stage is then always consumed by the same
-  // group, so no warp can be two barrier phases away from the one it waits for.
-  for (int s = kMaxStages; s >= 4; s -= 4)
+int max_stages(int K, int toks) {
+  for (int s = kMaxStages; s >= 1; --s)
     if (make_layout<MT, GROUP>(K, s, toks).total <= (uint32_t)kSmemLimit) return s;
   return 0;
 }
-int stages_for(const QmmArgs& a) {
+struct RingPlan { int stages, groups; };
+RingPlan plan_ring(const QmmArgs& a) {
   const int K = (int)a.K, ts = stored_tokens(a.M);
-  if (a.M <= 8) return a.group == 32 ? pick_stages<1, 32>(K, ts) : (a.group == 64 ? pick_stages<1, 64>(K, ts) : pick_stages<1, 128>(K, ts));
-  return a.group == 32 ? pick_stages<2, 32>(K, ts) : (a.group == 64 ? pick_stages<2, 64>(K, ts) : pick_stages<2, 128>(K, ts));
+  int m;
+  if (a.M <= 8) m = a.group == 32 ? max_stages<1, 32>(K, ts) : (a.group == 64 ? max_stages<1, 64>(K, ts) : max_stages<1, 128>(K, ts));
+  else m = a.group == 32 ? max_stages<2, 32>(K, ts) : (a.group == 64 ? max_stages<2, 64>(K, ts) : max_stages<2, 128>(K, ts));
+  if (m >= 8) return {8, 4};
+  if (m >= 4) return {m & ~1, 2};
+  return {0, 0};
 }
+int stages_for(const QmmArgs& a) { return plan_ring(a).stages; }
 
 size_t counters_bytes(int64_t N) { return (size_t)(((N + kRows - 1) / kRows * 4 + 255) / 256 * 256); }
 size_t slots_bytes() { return (size_t)kMaxCtas * 2 * kRows * 16 * 4; }
 
-template <int MT, int GROUP>
+template <int MT, int GROUP, int NG>
 int launch(const QmmArgs& a, const CUtensorMap& map_w, EncodeFn enc, SParams& p, int grid, cudaStream_t st) {
   // activations as a 3-D tensor (32 k, token, 32-k chunk): one box = all of x in staging order
   CUtensorMap map_x;
@@ -669,9 +692,9 @@ int launch(const QmmArgs& a, const CUtensorMap& map_w, EncodeFn enc, SParams& p,
     if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for x failed (%d)", (int)r);
   }
   const Layout L = make_layout<MT, GROUP>((int)a.K, p.stages, p.toks);
-  cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<MT, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
+  cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<MT, GROUP, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
   if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-  qmv_stream_kernel<MT, GROUP><<<grid, kThreads, L.total, st>>>(map_w, map_x, p);
+  qmv_stream_kernel<MT, GROUP, NG><<<grid, kThreads, L.total, st>>>(map_w, map_x, p);
   B200Q_LAUNCH_OK("qmv_stream_kernel");
   return B200Q_OK;
 }
@@ -736,9 +759,13 @@ int qmv_stream(const QmmArgs& a, cudaStream_t st) {
   long long grid = p.total < sms ? p.total : sms;
   if (grid > kMaxCtas) grid = kMaxCtas;
   const bool mt2 = a.M > 8;
-  if (a.group == 32) return mt2 ? launch<2, 32>(a, map_w, enc, p, (int)grid, st) : launch<1, 32>(a, map_w, enc, p, (int)grid, st);
-  if (a.group == 64) return mt2 ? launch<2, 64>(a, map_w, enc, p, (int)grid, st) : launch<1, 64>(a, map_w, enc, p, (int)grid, st);
-  return mt2 ? launch<2, 128>(a, map_w, enc, p, (int)grid, st) : launch<1, 128>(a, map_w, enc, p, (int)grid, st);
+  const bool g4 = plan_ring(a).groups == 4;
+#define B200Q_STREAM_LAUNCH(MT_, G_) \
+  (g4 ? launch<MT_, G_, 4>(a, map_w, enc, p, (int)grid, st) : launch<MT_, G_, 2>(a, map_w, enc, p, (int)grid, st))
+  if (a.group == 32) return mt2 ? B200Q_STREAM_LAUNCH(2, 32) : B200Q_STREAM_LAUNCH(1, 32);
+  if (a.group == 64) return mt2 ? B200Q_STREAM_LAUNCH(2, 64) : B200Q_STREAM_LAUNCH(1, 64);
+  return mt2 ? B200Q_STREAM_LAUNCH(2, 128) : B200Q_STREAM_LAUNCH(1, 128);
+#undef B200Q_STREAM_LAUNCH
 }
 
 }  // namespace b200q
