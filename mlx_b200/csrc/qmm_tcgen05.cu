@@ -44,7 +44,10 @@ namespace {
 constexpr int kTileN = 128;       // weight rows per tile (MMA M)
 constexpr int kBlockK = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
 constexpr int kStagesA = 8;       // A ring in TMEM (32 columns each)
-constexpr int kStagesB = 4;       // x tiles in shared memory
+constexpr int kMaxStagesB = 6;
+// x tiles in shared memory.  Six stages fit next to the packed ring for bits <= 4 but measured
+// slower (474 us against 443 us on M=4096, N=14336, K=4096): four it is.
+__host__ __device__ constexpr int stages_b(int) { return 4; }
 constexpr int kStagesP = 4;       // packed W tiles in shared memory
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
@@ -102,7 +105,7 @@ struct TcParams {
 
 struct __align__(8) Barriers {
   uint64_t full_p[kStagesP], empty_p[kStagesP];
-  uint64_t full_b[kStagesB], empty_b[kStagesB];
+  uint64_t full_b[kMaxStagesB], empty_b[kMaxStagesB];
   uint64_t full_a[kStagesA], empty_a[kStagesA];
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
@@ -197,6 +200,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   // A packed stage holds 128 k of every row (16*BITS bytes, a multiple of 16 for every width)
   // and feeds two 64-k MMA blocks.
   constexpr int kPRowBytes = 16 * BITS;
+  constexpr int kStagesB = stages_b(BITS);
   constexpr int kPStageBytes = kTileN * kPRowBytes;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // carve-up: [B ring: kStagesB * NT*128 B (1024-aligned)] [P ring: kStagesP * 4096 B] [barriers]
@@ -494,7 +498,7 @@ int pick_nt(int64_t M) {
 
 size_t smem_bytes(int nt, int bits) {
   const size_t b_pitch = ((size_t)nt * 128 + 1023) & ~size_t(1023);
-  const size_t need = 1024 + kStagesB * b_pitch + (size_t)kStagesP * kTileN * 16 * bits + sizeof(Barriers) + 64;
+  const size_t need = 1024 + stages_b(bits) * b_pitch + (size_t)kStagesP * kTileN * 16 * bits + sizeof(Barriers) + 64;
   // More than half of an SM's shared memory: guarantees one CTA per SM, so the 512-column
   // tensor-memory allocation never has to wait for a co-resident CTA of this kernel.
   const size_t one_per_sm = 120 * 1024;

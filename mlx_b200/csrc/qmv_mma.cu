@@ -189,6 +189,13 @@ qmv_mma_kernel(const QmvParams p) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
+  {
+    // The first mma.sync of a kernel is slow (the tensor pipe wakes up): issue one now, while the
+    // first loads are in flight anyway.  Its result is never used.
+    float d0, d1, d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
+                 : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
+  }
   const long long T = p.total_steps;  // < 2^31 (checked on the host)
   const int G = gridDim.x;
   const int ksteps = p.ksteps;
@@ -243,31 +250,34 @@ qmv_mma_kernel(const QmvParams p) {
   // ---- stage x in B-fragment order; zero the tile buffer -------------------------
   {
     constexpr int U = 8;  // loads in flight per thread
-    const int items = MT * ksteps * 128;
-    for (int base = tid; base < items; base += kThreads * U) {
-      uint4 v[U];
+    const int per_mt = ksteps * 128;   // items of one 8-token half: [ksteps][4][32]
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int i = base + u * kThreads;
-        v[u] = make_uint4(0, 0, 0, 0);
-        if (i < items) {
-          const int ln = i & 31, c = (i >> 5) & 3;
-          const int kb = (i >> 7) % ksteps, mt = (i >> 7) / ksteps;
-          const int tok = mt * 8 + (ln >> 2);
-          const int k8 = kb * 128 + 32 * (ln & 3) + 8 * c;
-          if (tok < p.M) v[u] = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)tok * p.K + k8));
+    for (int mt = 0; mt < MT; ++mt) {
+      uint4* xs_mt = xs + (size_t)mt * per_mt;
+      for (int base = tid; base < per_mt; base += kThreads * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = base + u * kThreads;
+          v[u] = make_uint4(0, 0, 0, 0);
+          if (j < per_mt) {
+            const int ln = j & 31, c = (j >> 5) & 3, kb = j >> 7;
+            const int tok = mt * 8 + (ln >> 2);
+            const int k8 = kb * 128 + 32 * (ln & 3) + 8 * c;
+            if (tok < p.M) v[u] = __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)tok * p.K + k8));
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int i = base + u * kThreads;
-        if (i < items) {
-          uint4 o;
-          o.x = __byte_perm(v[u].x, v[u].z, 0x5410);  // (x0, x4)
-          o.y = __byte_perm(v[u].x, v[u].z, 0x7632);  // (x1, x5)
-          o.z = __byte_perm(v[u].y, v[u].w, 0x5410);  // (x2, x6)
-          o.w = __byte_perm(v[u].y, v[u].w, 0x7632);  // (x3, x7)
-          xs[i] = o;
+        for (int u = 0; u < U; ++u) {
+          const int j = base + u * kThreads;
+          if (j < per_mt) {
+            uint4 o;
+            o.x = __byte_perm(v[u].x, v[u].z, 0x5410);  // (x0, x4)
+            o.y = __byte_perm(v[u].x, v[u].z, 0x7632);  // (x1, x5)
+            o.z = __byte_perm(v[u].y, v[u].w, 0x5410);  // (x2, x6)
+            o.w = __byte_perm(v[u].y, v[u].w, 0x7632);  // (x3, x7)
+            xs_mt[j] = o;
+          }
         }
       }
     }

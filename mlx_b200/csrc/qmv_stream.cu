@@ -248,6 +248,13 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   const int S = p.stages;
   const int row_groups = p.K / GROUP;
 
+  {
+    // The first mma.sync of a kernel takes a couple of thousand cycles (the tensor pipe wakes up):
+    // issue one now, while nothing else can run anyway.  Its result is never used.
+    float d0, d1, d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
+                 : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
+  }
   if (tid == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   if (tid == 64) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
   if (tid == 0) {
