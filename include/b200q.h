@@ -214,6 +214,18 @@ int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_
 int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream);
 
 /*
+ * K-sharded linear with the all_reduce fused into the exchange (QuantizedShardedToAllLinear of
+ * the reference, python/mlx/nn/layers/distributed.py:490-588: matmul over this rank's slice of
+ * the input dimension, then all_sum, mlx/distributed/nccl/nccl.cpp:389-406).  Every rank calls
+ * b200q_qmm_sharded with y_peers[q] = slot `rank` of rank q's buffer (ld = N, col0 = 0), so its
+ * partial [M, N] lands in every rank; after b200q_peer_signal / b200q_peer_wait,
+ * b200q_peer_reduce adds this rank's n_slots slots (each `stride` elements apart, n = M * N
+ * used) in fp32, in slot order, and rounds once to the output type: all ranks get identical
+ * results.
+ */
+int b200q_peer_reduce(const void* slots, int n_slots, int64_t stride, int64_t n, void* y, int dtype, void* stream);
+
+/*
  * Set-up helpers for the peer buffers (not capture-safe, they allocate): a buffer that
  * other processes on the same machine can map (cudaMalloc + cudaIpcGetMemHandle), and
  * the mapping of another process's buffer into this one (cudaIpcOpenMemHandle with lazy

@@ -40,6 +40,7 @@ SIGNATURES = {
                                       _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_peer_signal": (_i, [_vp, _i, _vp, _vp]),
     "b200q_peer_wait": (_i, [_vp, _vp, _vp, _vp]),
+    "b200q_peer_reduce": (_i, [_vp, _i, _i64, _i64, _vp, _i, _vp]),
     "b200q_ipc_alloc": (_i, [_sz, _vp, _vp]),
     "b200q_ipc_open": (_i, [_vp, _vp]),
     "b200q_ipc_close": (_i, [_vp]),

@@ -32,7 +32,7 @@ void count_launch(int n) { g_launches += (uint64_t)n; }
 
 namespace {
 
-enum class Path { QmvStream, QmvTc, QmvBulk, Qmv, Tc, Generic };
+enum class Path { QmvStream, QmvTc, QmvBulk, Qmv, Tc, Qvm, Generic };
 
 int check_qmm_args(const char* tag, const QmmArgs& a) {
   if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
@@ -83,6 +83,7 @@ Path choose(const QmmArgs& a) {
   if (qmv_mma_supported(a)) return Path::Qmv;
   if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
   if (qmm_tc_supported(a)) return Path::Tc;
+  if (qvm_supported(a)) return Path::Qvm;
   return Path::Generic;
 }
 
@@ -116,6 +117,7 @@ int run_qmm(const QmmArgs& a, cudaStream_t st) {
     case Path::QmvBulk: return qmv_bulk(a, st);
     case Path::Qmv: return qmv_mma(a, st);
     case Path::Tc: return qmm_tc(a, st);
+    case Path::Qvm: return qvm(a, st);
     default: return qmm_generic(a, st);
   }
 }
@@ -145,6 +147,10 @@ extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M,
   q = q > qs ? q : qs;
   size_t t = qmm_tc_workspace_bytes(a);
   need = q > t ? q : t;
+  if (!transpose) {
+    const size_t v = qvm_workspace_bytes(a);
+    need = need > v ? need : v;
+  }
   return (need + 255) / 256 * 256;
 }
 
@@ -169,6 +175,7 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
     case Path::QmvBulk: return "qmv_bulk";
     case Path::Qmv: return "qmv_mma";
     case Path::Tc: return "qmm_tcgen05";
+    case Path::Qvm: return "qvm";
     default: return "qmm_generic";
   }
 }
@@ -200,6 +207,28 @@ __global__ void peer_wait_kernel(const uint32_t* flag, const uint32_t* epoch, ui
     }
     __nanosleep(200);
   }
+}
+// y[i] = sum over the n_slots partial results slots[r * stride + i], added in fp32 in slot order,
+// rounded once to T.  Eight elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) peer_reduce_kernel(const T* __restrict__ slots, int n_slots, int64_t stride,
+                                                          int64_t n, T* __restrict__ y) {
+  const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= n) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const bool full = i0 + 8 <= n && (((uintptr_t)slots | (uintptr_t)y | (uintptr_t)(stride * sizeof(T))) & 15) == 0;
+  for (int r = 0; r < n_slots; ++r) {
+    const T* p = slots + r * stride + i0;
+    if (full && sizeof(T) == 2) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += Elem<T>::to_float(e[j]);
+    } else {
+      for (int j = 0; j < 8 && i0 + j < n; ++j) acc[j] += Elem<T>::to_float(p[j]);
+    }
+  }
+  for (int j = 0; j < 8 && i0 + j < n; ++j) y[i0 + j] = Elem<T>::from_float(acc[j]);
 }
 }  // namespace peer
 }  // namespace b200q
@@ -245,6 +274,24 @@ extern "C" int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch
   if (!flag_local || !epoch_local || !status) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_wait] null pointer");
   peer::peer_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag_local, epoch_local, status);
   B200Q_LAUNCH_OK("peer_wait_kernel");
+  return B200Q_OK;
+}
+
+extern "C" int b200q_peer_reduce(const void* slots, int n_slots, int64_t stride, int64_t n, void* y, int dtype, void* stream) {
+  if (!slots || !y || n_slots < 1 || n_slots > kMaxPeers || stride < n || n < 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_reduce] between 1 and %d slots of at least n elements each are required", kMaxPeers);
+  if (n == 0) return B200Q_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)((n + 8 * 256 - 1) / (8 * 256));
+  if (dtype == B200Q_BF16)
+    peer::peer_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)slots, n_slots, stride, n, (__nv_bfloat16*)y);
+  else if (dtype == B200Q_F16)
+    peer::peer_reduce_kernel<__half><<<grid, 256, 0, st>>>((const __half*)slots, n_slots, stride, n, (__half*)y);
+  else if (dtype == B200Q_F32)
+    peer::peer_reduce_kernel<float><<<grid, 256, 0, st>>>((const float*)slots, n_slots, stride, n, (float*)y);
+  else
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_reduce] Only real floating types are supported (dtype code %d).", dtype);
+  B200Q_LAUNCH_OK("peer_reduce_kernel");
   return B200Q_OK;
 }
 

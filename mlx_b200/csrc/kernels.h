@@ -70,6 +70,11 @@ bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a);
 int qmv_mma(const QmmArgs& a, cudaStream_t st);
 
+// qvm.cu : non-transposed decode (M <= 4, bits 2/4/8): y = x * dequant(W[K, N])
+bool qvm_supported(const QmmArgs& a);
+size_t qvm_workspace_bytes(const QmmArgs& a);
+int qvm(const QmmArgs& a, cudaStream_t st);
+
 // qmv_stream.cu : decode path for 4-bit weights (TMA ring, ldmatrix, exact factorised form)
 bool qmv_stream_supported(const QmmArgs& a);
 bool qmv_stream_profitable(const QmmArgs& a);   // large enough to beat qmv_mma

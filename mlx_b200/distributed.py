@@ -237,3 +237,84 @@ def sharded_gather_qmm(x: torch.Tensor, w_local: torch.Tensor, scales_local: tor
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
     _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     return out.local(buf, n_idx * M).view(n_idx, M, N)
+
+
+# ---------------------------------------------------------------------------------------------
+# K-sharded linear (QuantizedShardedToAllLinear of the reference,
+# python/mlx/nn/layers/distributed.py:490-588): rank r multiplies its slice of the input
+# dimension, then the partial outputs are summed over the ranks (all_sum).
+# ---------------------------------------------------------------------------------------------
+def shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """The slice of the last axis owned by `rank` (packed weight words or scale groups)."""
+    lo, hi = shard_bounds(t.shape[-1], rank, world)
+    return t[..., lo:hi].contiguous()
+
+
+class QuantizedShardedToAllLinear:
+    """y = sum over ranks of x[..., k-slice] @ dequant(W[:, k-slice])^T."""
+
+    def __init__(self, weight: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64,
+                 bits: int = 4, group: Optional[dist.ProcessGroup] = None, rank: Optional[int] = None,
+                 world: Optional[int] = None, already_sharded: bool = False):
+        if rank is None or world is None:
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.group, self.rank, self.world = group, rank, world
+        self.group_size, self.bits = group_size, bits
+        if already_sharded:
+            self.weight, self.scales, self.biases = weight, scales, biases
+        else:
+            if scales.shape[-1] % world != 0:
+                raise ValueError(f"cannot shard {scales.shape[-1]} quantization groups evenly across {world} ranks")
+            self.weight = shard_cols(weight, rank, world)
+            self.scales = shard_cols(scales, rank, world)
+            self.biases = shard_cols(biases, rank, world)
+        self.n_out = self.weight.shape[-2]
+        self.k_local = self.scales.shape[-1] * group_size
+
+    def x_slice(self, x: torch.Tensor) -> torch.Tensor:
+        return x[..., self.rank * self.k_local:(self.rank + 1) * self.k_local].contiguous()
+
+    def partial(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.quantized_matmul(self.x_slice(x), self.weight, self.scales, self.biases, transpose=True,
+                                    group_size=self.group_size, bits=self.bits)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """Partial matmul + all_reduce through the process group (the reference's formulation)."""
+        y = self.partial(x)
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
+
+
+def sharded_matmul_allreduce(layer: QuantizedShardedToAllLinear, x: torch.Tensor, out: PeerOutput) -> torch.Tensor:
+    """The same result with the exchange fused into the matmul: every rank's kernel stores its
+    partial [M, N] into slot `rank` of every rank's buffer (peer stores), then one flag update, one
+    bounded wait and a local fp32 sum over the slots.  `out` must hold world * M rows of N columns
+    (`PeerOutput(world * m_max, N)`).  x: [M, K] bf16 CUDA, the same on every rank."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
+        raise ValueError("[sharded_matmul_allreduce] x must be a 2-D bfloat16 CUDA tensor")
+    M = x.shape[0]
+    N, R = layer.n_out, out.world
+    if N != out.n_total or R * M > out.m_max:
+        raise ValueError("[sharded_matmul_allreduce] output buffers do not match the layer")
+    lib = out.lib
+    xs = layer.x_slice(x)
+    K = xs.shape[1]
+    dt = _lib.BF16
+    need = max(int(lib.b200q_qmm_workspace_bytes(dt, 1, M, N, K, layer.group_size, layer.bits, 1)), 256)
+    ws = ops._workspaces.get(x.device, need, "qmm")
+    st = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    buf = out.step % out.N_BUF
+    slot_bytes = M * N * 2
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    ys = (ctypes.c_void_p * R)(*[b + buf * out.buf_bytes + out.rank * slot_bytes for b in out.base])
+    _lib.check(lib.b200q_qmm_sharded(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M, N, K,
+                                     layer.group_size, layer.bits, vp(ws), ws.numel(), st))
+    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), R, ctypes.c_void_p(out.epoch), st))
+    out.step += 1
+    status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
+    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.b200q_peer_reduce(ctypes.c_void_p(out._own + buf * out.buf_bytes), R, M * N, M * N, vp(y), dt, st))
+    return y

@@ -13,8 +13,8 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 import mlx_b200 as mb  # noqa: E402
 import oracle as O  # noqa: E402
 from mlx_b200 import _lib, ops  # noqa: E402
-from mlx_b200.distributed import (PeerOutput, QuantizedAllToShardedLinear, expert_bounds, sharded_gather_qmm,  # noqa: E402
-                                  sharded_matmul_allgather)
+from mlx_b200.distributed import (PeerOutput, QuantizedAllToShardedLinear, QuantizedShardedToAllLinear,  # noqa: E402
+                                  expert_bounds, sharded_gather_qmm, sharded_matmul_allgather, sharded_matmul_allreduce)
 from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch  # noqa: E402
 
 
@@ -63,6 +63,27 @@ def main():
         ok = ok and good
         dist.barrier()
     out2.close()
+
+    # ---- K-sharded linear: partial products summed over the ranks (fused exchange)
+    N3, K3 = 512, 2048
+    wq3, s3, b3 = O.quantize(make_w(9, (N3, K3), "bf16"), g, 4, "bf16")
+    down = QuantizedShardedToAllLinear(u32_to_torch(wq3), to_torch(s3, "bf16"), to_torch(b3, "bf16"), g, 4, rank=rank, world=world)
+    out3 = PeerOutput(world * 40, N3)
+    for step, M in enumerate((16, 40, 3)):
+        x3 = make_x(30 + step, (M, K3), "bf16")
+        y3 = sharded_matmul_allreduce(down, to_torch(x3, "bf16"), out3)
+        torch.cuda.synchronize()
+        ref3 = O.qmm_f32_from(x3, wq3, s3, b3, "bf16", transpose=True, group_size=g, bits=4)
+        good, rel = qmm_close(O.to_f32(from_torch(y3), "bf16"), ref3)
+        # every rank must hold bit-identical results (same slots, same order of additions)
+        mine = y3.view(torch.int16).cpu()
+        both = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        same = all(torch.equal(both[0], t) for t in both)
+        print(f"rank {rank} allreduce step {step} M={M} ok={good} rel={rel:.4f} identical={same}", flush=True)
+        ok = ok and good and same
+        dist.barrier()
+    out3.close()
     dist.destroy_process_group()
     print(f"rank {rank} {'PEER-OK' if ok else 'PEER-FAIL'}", flush=True)
     sys.exit(0 if ok else 1)

@@ -69,6 +69,8 @@ def test_kernel_selection_names():
     assert name(16, 14336, 4096, bits=3) == "qmv_mma"
     assert name(16, 14336, 4096, dt=_lib.F32) == "qmm_generic"
     assert name(16, 4096, 4096, tr=0) == "qmm_generic"
+    assert name(1, 4096, 4096, tr=0) == "qvm" and name(4, 4096, 4096, tr=0, bits=8) == "qvm"
+    assert name(2, 4096, 4096, tr=0, bits=3) == "qmm_generic"
     assert name(4, 100, 96, g=32) == "qmm_generic"
     assert lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, 16, 14336, 4096, 64, 4, 1) > 14336 * 64
 

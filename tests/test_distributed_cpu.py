@@ -37,6 +37,19 @@ def _worker(rank, world, port, ret):
     # batched leading dims
     y3 = all_gather_columns(torch.from_numpy(np.stack([y_r, 2 * y_r])), None, world).numpy()
     ok = ok and bool(np.array_equal(y3[1], 2 * full))
+    # K-sharded layer: column slices of the packed words / scale groups, partial products, all_sum
+    from mlx_b200.distributed import QuantizedShardedToAllLinear
+    layer = QuantizedShardedToAllLinear(torch.from_numpy(wq.view(np.int32)), torch.from_numpy(s), torch.from_numpy(b), g, bits,
+                                        rank=rank, world=world)
+    klo, khi = rank * K // world, (rank + 1) * K // world
+    assert layer.k_local == K // world and tuple(layer.weight.shape) == (N, (K // world) * bits // 32)
+    assert np.array_equal(layer.weight.numpy().view(np.uint32), wq[:, klo * bits // 32:khi * bits // 32])
+    xs = layer.x_slice(torch.from_numpy(x)).numpy()
+    assert np.array_equal(xs, x[:, klo:khi])
+    part = O.qmm(xs, layer.weight.numpy().view(np.uint32), layer.scales.numpy(), layer.biases.numpy(), True, g, bits, "f32")
+    tot = torch.from_numpy(part.copy())
+    dist.all_reduce(tot)
+    ok = ok and bool(np.allclose(tot.numpy(), full, rtol=1e-5, atol=1e-5))
     ret[rank] = ok
     dist.destroy_process_group()
 

@@ -221,3 +221,22 @@ def test_tcgen05_prefill_full_size_sampled_rows():
     ref2 = O.qmm_f32_from(x[seam_rows], wq, s, b, dtype, transpose=True, group_size=64, bits=4)
     ok, rel = qmm_close(O.to_f32(from_torch(y[torch.from_numpy(seam_rows).cuda()]), dtype), ref2)
     assert ok, rel
+
+
+# ---- non-transposed decode (qvm): y = x @ dequant(W[K, N]) -----------------------------------
+@pytest.mark.parametrize("dtype", ("bf16", "f16", "f32"))
+@pytest.mark.parametrize("bits,g", [(4, 64), (8, 32), (2, 128)])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (4, 1536, 1000), (2, 64, 7), (3, 14336, 512)])
+def test_qvm_no_transpose(dtype, bits, g, M, N, K):
+    if N % g:
+        pytest.skip("N must be a multiple of the group size")
+    rel = run_case(dtype, M, N, K, g, bits, transpose=False, seed=M + K, expect_kernel=("qvm",))
+    assert rel < 2e-2
+
+
+def test_qvm_then_transposed_decode_share_workspace():
+    """The split-K slots of the non-transposed kernel must be left zeroed for the kernels that
+    accumulate into the same workspace."""
+    for _ in range(2):
+        run_case("bf16", 2, 4096, 2048, 64, 4, transpose=False, seed=11, expect_kernel=("qvm",))
+        run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_mma", "qmv_stream"))
