@@ -7,8 +7,9 @@
 //    load), a warp 512 columns (256..1024 contiguous bytes per row and request), the 8 warps
 //    of a CTA take every 8th row of the CTA's slab of K, and gridDim.y slabs split K so that
 //    about two CTAs per SM exist whatever N is.
-//  * Fields become floats without a conversion instruction: (q << 15) | 0x43800000 is the
-//    float 256 + q, so acc += (x s)(256 + q) and 256 * sum(x s) is taken off at the end,
+//  * Fields become floats without a conversion instruction: q in the top `bits` mantissa bits
+//    of the float 2^bits is 2^bits + q, so acc += (x s)(2^bits + q) and 2^bits * sum(x s) is taken
+//    off at the end,
 //    together with sum(x b) for the biases (one scale and bias per lane and row: 16 columns
 //    never straddle a group).
 //  * The warps of a CTA add their columns in a shared tile; with one slab the tile is rounded
@@ -53,8 +54,12 @@ qvm_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq, const T* __
            const T* __restrict__ biases, T* __restrict__ y, float* __restrict__ partial, uint32_t* __restrict__ counters,
            int M, int N, int K, int group, int slab) {
   constexpr int NW = BITS / 2;              // 32-bit words holding a lane's 16 fields
-  constexpr uint32_t kMagic = 0x43800000u;  // 256.0f: fields go to mantissa bits [22:15]
-  constexpr uint32_t kMask = ((1u << BITS) - 1u) << 15;
+  // 2^BITS as a float with the field in the top BITS mantissa bits is the float 2^BITS + q; the
+  // smallest offset that works keeps the cancellation against sum(x s) * 2^BITS small.
+  constexpr int kPos = 23 - BITS;                                    // field goes to bits [kPos, 23)
+  constexpr uint32_t kMagic = (uint32_t)(127 + BITS) << 23;          // 2^BITS
+  constexpr float kOffset = (float)(1 << BITS);
+  constexpr uint32_t kMask = ((1u << BITS) - 1u) << kPos;
   extern __shared__ float smem[];
   float* xs = smem;                          // [kQvmMaxM][slab]
   float* tile = smem + kQvmMaxM * slab;      // [kQvmMaxM][kQvmCols]
@@ -106,7 +111,7 @@ qvm_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq, const T* __
         constexpr int per_word = 32 / BITS;
         const uint32_t word = w[j / per_word];
         const int sh = (j % per_word) * BITS;          // field at bits [sh, sh + BITS)
-        const uint32_t moved = sh >= 15 ? (word >> (sh - 15)) : (word << (15 - sh));
+        const uint32_t moved = sh >= kPos ? (word >> (sh - kPos)) : (word << (kPos - sh));
         q[j] = __uint_as_float((moved & kMask) | kMagic);
       }
 #pragma unroll
@@ -121,7 +126,7 @@ qvm_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq, const T* __
     }
 #pragma unroll
     for (int m = 0; m < MM; ++m) {
-      const float fix = fmaf(-256.0f, sum_xs[m], sum_xb[m]);
+      const float fix = fmaf(-kOffset, sum_xs[m], sum_xb[m]);
 #pragma unroll
       for (int j = 0; j < 16; ++j) atomicAdd(&tile[m * kQvmCols + lane * 16 + j], acc[m][j] + fix);
     }
