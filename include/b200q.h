@@ -238,6 +238,18 @@ int b200q_ipc_close(void* ptr);
 int b200q_ipc_free(void* ptr);
 
 /*
+ * GGUF quantized tensors -> this library's affine layout, on the device (group size 32;
+ * 4-bit for Q4_0 / Q4_1, 8-bit for Q8_0; float16 scales and biases).  Replaces the host-side
+ * repack of the reference's loader (mlx/io/gguf_quants.cpp:11-102).  `blocks` is the tensor's
+ * raw block data (n_blocks blocks of 18 / 20 / 34 bytes, 2-byte aligned), gguf_type the GGUF
+ * type id (2 = Q4_0, 3 = Q4_1, 8 = Q8_0).  Outputs: wq n_blocks*4 (4-bit) or n_blocks*8 (8-bit)
+ * words, scales and biases n_blocks float16 each; a [rows, K] tensor has K/32 consecutive
+ * blocks per row, so the outputs are already [rows, K*bits/32] and [rows, K/32].
+ */
+int b200q_gguf_repack(const void* blocks, int gguf_type, int64_t n_blocks, uint32_t* wq, void* scales,
+                      void* biases, void* stream);
+
+/*
  * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
  * launch for this problem ("qmv_mma", "qmv_stream", "qmv_bulk", "qmv_tc", "qmm_tcgen05",
  * "qmm_generic").

@@ -10,7 +10,7 @@ root when present, else 6650 GB/s / 1590 TFLOP/s).
 Cases: C1 decode GEMV (M=1, 4096x4096), C2 small-batch decode (M=16, 14336x4096), C3 prefill
 (M=4096), C4 bit-width / group sweep on the 70B-MLP shape (K=8192, N=28672; bits 3/6/8 x group
 32/128 at M 1 and 512) plus quantize / dequantize of that matrix, C5 Mixtral-style gather_qmm
-(8 experts, 512 tokens, top-2).  Inputs are seeded synthetic draws (x ~ N(0,1), W ~ N(0,0.02)).
+(8 experts, 512 tokens, top-2), T0 the non-transposed decode form.  Inputs are seeded synthetic draws (x ~ N(0,1), W ~ N(0,0.02)).
 """
 from __future__ import annotations
 
@@ -68,31 +68,32 @@ def make_weights(N, K, bits, group, copies, seed=2):
     return out
 
 
-def qmm_case(tag, M, N, K, bits, group, iters):
+def qmm_case(tag, M, N, K, bits, group, iters, transpose=True):
     lib = _lib.load()
     hbm, tf, src = peaks()
     wbytes = N * K * bits // 8 + 4 * N * K // group
     copies = max(1, min(16, int(np.ceil(2 * 126e6 / wbytes)))) if M <= 64 else 1
-    ws_list = make_weights(N, K, bits, group, copies)
+    ws_list = make_weights(N, K, bits, group, copies) if transpose else make_weights(K, N, bits, group, copies)
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
     y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    need = max(int(lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, M, N, K, group, bits, 1)), 256)
+    tr = 1 if transpose else 0
+    need = max(int(lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, M, N, K, group, bits, tr)), 256)
     ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
     st = torch.cuda.Stream()
     sp = ctypes.c_void_p(st.cuda_stream)
 
     def call(i):
         q, s, b = ws_list[i % copies]
-        rc = lib.b200q_qmm(P(x), P(q), P(s), P(b), P(y), _lib.BF16, 1, M, N, K, group, bits, 1, 0, P(ws), ws.numel(), sp)
+        rc = lib.b200q_qmm(P(x), P(q), P(s), P(b), P(y), _lib.BF16, 1, M, N, K, group, bits, tr, 0, P(ws), ws.numel(), sp)
         if rc:
             raise RuntimeError(_lib.last_error())
 
     t = graph_time(call, iters, st)
     B = wbytes + M * K * 2 + M * N * 2
     F = 2.0 * M * N * K
-    rec = {"case": tag, "op": "quantized_matmul", "M": M, "N": N, "K": K, "bits": bits, "group": group,
-           "kernel": lib.b200q_qmm_kernel_name(_lib.BF16, 1, M, N, K, group, bits, 1).decode(), "us": t * 1e6,
+    rec = {"case": tag, "op": "quantized_matmul" if transpose else "quantized_matmul(transpose=False)", "M": M, "N": N, "K": K, "bits": bits, "group": group,
+           "kernel": lib.b200q_qmm_kernel_name(_lib.BF16, 1, M, N, K, group, bits, tr).decode(), "us": t * 1e6,
            "GBps": B / t / 1e9, "TFLOPs": F / t / 1e12, "frac_hbm": B / t / 1e9 / hbm, "frac_tensor": F / t / 1e12 / tf,
            "weight_copies": copies, "peaks": src}
     print(json.dumps(rec), flush=True)
@@ -171,6 +172,11 @@ def main():
         for bits, group in ((3, 32), (6, 128), (8, 32), (4, 64)):
             quant_case("C4", 28672, 8192, bits, group, 4)
     gather_case("C5", 8, 512, 2, 14336, 4096, 4, 64, max(it // 4, 3))
+    if not a.quick:
+        # the non-transposed form (vector-Jacobian product of the decode matmul)
+        qmm_case("T0", 1, 4096, 4096, 4, 64, it, transpose=False)
+        qmm_case("T0", 1, 28672, 8192, 4, 64, 10, transpose=False)
+        qmm_case("T0", 4, 4096, 14336, 8, 64, 10, transpose=False)
 
 
 if __name__ == "__main__":

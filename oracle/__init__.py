@@ -59,7 +59,8 @@ def _load():
         lib.qref_dequantize.argtypes = [vp, vp, vp, i32, sz, i32, i32, vp]
         lib.qref_qmm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32]
         lib.qref_gather_qmm.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, i32, i32, i32, i32, i32, i32, i32]
-        for f in (lib.qref_quantize, lib.qref_dequantize, lib.qref_qmm, lib.qref_gather_qmm):
+        lib.qref_gguf_repack.argtypes = [vp, i32, sz, vp, vp, vp]
+        for f in (lib.qref_quantize, lib.qref_dequantize, lib.qref_qmm, lib.qref_gather_qmm, lib.qref_gguf_repack):
             f.restype = i32
         _lib = lib
     return _lib
@@ -232,3 +233,22 @@ def ref_gather_qmm(x, wq, scales, biases, lhs, rhs, transpose=True, group_size=6
         {"y": (_NP[dtype], (lhs.size, M, N))},
     )
     return outs["y"]
+
+
+# ----------------------------------------------------------------------------- GGUF repack
+GGUF_BLOCK_BYTES = {2: 18, 3: 20, 8: 34}   # Q4_0, Q4_1, Q8_0
+
+
+def gguf_repack(blocks: np.ndarray, gguf_type: int):
+    """blocks uint8 [n_blocks, block_bytes] -> (wq uint8 [n_blocks, 16 or 32], scales, biases as
+    float16 bit patterns uint16 [n_blocks]); restates mlx/io/gguf_quants.cpp:11-102."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    n = blocks.shape[0]
+    per = 16 if gguf_type in (2, 3) else 32
+    wq = np.zeros((n, per), dtype=np.uint8)
+    s = np.zeros(n, dtype=np.uint16)
+    b = np.zeros(n, dtype=np.uint16)
+    rc = _load().qref_gguf_repack(_p(blocks), gguf_type, n, _p(wq), _p(s), _p(b))
+    if rc != 0:
+        raise ValueError(f"qref_gguf_repack: unsupported type {gguf_type}")
+    return wq, s, b
