@@ -247,7 +247,9 @@ def sharded_gather_qmm(x: torch.Tensor, w_local: torch.Tensor, scales_local: tor
 def shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     """The slice of the last axis owned by `rank` (packed weight words or scale groups)."""
     lo, hi = shard_bounds(t.shape[-1], rank, world)
-    return t[..., lo:hi].contiguous()
+    if t.dtype == torch.uint32:   # torch has no strided copy for uint32: go through the int32 view
+        return t.view(torch.int32).narrow(-1, lo, hi - lo).contiguous().view(torch.uint32)
+    return t.narrow(-1, lo, hi - lo).contiguous()
 
 
 class QuantizedShardedToAllLinear:
