@@ -76,7 +76,7 @@ def main():
         ref3 = O.qmm_f32_from(x3, wq3, s3, b3, "bf16", transpose=True, group_size=g, bits=4)
         good, rel = qmm_close(O.to_f32(from_torch(y3), "bf16"), ref3)
         # every rank must hold bit-identical results (same slots, same order of additions)
-        mine = y3.view(torch.int16).cpu()
+        mine = y3.view(torch.int16).cpu().to(torch.int32)   # gloo has no int16 collectives
         both = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(both, mine)
         same = all(torch.equal(both[0], t) for t in both)
