@@ -164,6 +164,24 @@ int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const void* scale
                             int bits, void* stream);
 
 /*
+ * Two chained gather_qmm over the same index pairs (the expert MLP of a mixture-of-experts
+ * block as the reference benchmarks it, benchmarks/python/gather_qmm_bench.py:52-63):
+ *   h[i] = x[lhs_idx[i]] * dequant(w1[rhs_idx[i]])^T    (M x N1, rounded to bfloat16)
+ *   y[i] = h[i]          * dequant(w2[rhs_idx[i]])^T    (M x N2)
+ * The index pairs are sorted by expert once, the first product leaves its rows in expert
+ * order in the workspace and the second reads them there: one sort, one row gather and one
+ * scatter instead of two of each.  w1 [E, N1, K1*bits/32], w2 [E, N2, N1*bits/32]; bfloat16,
+ * transpose form, K1 and N1 multiples of 128 (B200Q_ERR_UNSUPPORTED otherwise: call
+ * b200q_gather_qmm twice).  Index checks and status word as b200q_gather_qmm.
+ */
+size_t b200q_gather_qmm_chain_workspace_bytes(int64_t n_idx, int64_t E, int64_t M, int64_t N1, int64_t K1);
+int b200q_gather_qmm_chain(const void* x, const uint32_t* wq1, const void* scales1, const void* biases1,
+                           const uint32_t* wq2, const void* scales2, const void* biases2,
+                           const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* y, int dtype,
+                           int64_t x_batch, int64_t E, int64_t M, int64_t N1, int64_t K1, int64_t N2,
+                           int group_size, int bits, void* ws, size_t ws_bytes, void* stream);
+
+/*
  * N-sharded linear with the all_gather fused into the matmul epilogue.  Replaces the pair
  * QuantizedAllToShardedLinear.__call__ + all_gather of the reference
  * (python/mlx/nn/layers/distributed.py:357-455, mlx/distributed/ops.cpp:62-84,

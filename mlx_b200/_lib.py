@@ -31,6 +31,9 @@ SIGNATURES = {
     "b200q_gather_qmm_workspace_bytes": (_sz, [_i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i]),
     "b200q_gather_qmm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i64, _i64, _i64, _i64, _i64,
                               _i, _i, _i, _i, _vp, _sz, _vp]),
+    "b200q_gather_qmm_chain_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200q_gather_qmm_chain": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i64, _i64, _i64, _i64, _i64,
+                                    _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_workspace_init": (_i, [_vp, _sz, _vp]),
     "b200q_read_status": (_i, [_vp, _sz, _vp, ctypes.POINTER(ctypes.c_uint32)]),
     "b200q_qmm_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i, _i, _i, _vp, _sz, _vp]),

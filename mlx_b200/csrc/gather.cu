@@ -262,3 +262,59 @@ extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local,
   return run_grouped(x, wq_local, scales_local, biases_local, lhs_idx, rhs_idx, n_idx, y_peers[self], &peers, x_batch, E_total,
                      e_lo, E_local, M, N, K, group_size, bits, ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------- two chained gather_qmm, one sort
+extern "C" size_t b200q_gather_qmm_chain_workspace_bytes(int64_t n_idx, int64_t E, int64_t M, int64_t N1, int64_t K1) {
+  if (n_idx < 1 || E < 1 || M < 1 || N1 < 1 || K1 < 1) return 256;
+  const FastLayout L = fast_layout(n_idx, E, M, K1);
+  return L.total + align256((size_t)L.n_rows * N1 * 2);
+}
+
+extern "C" int b200q_gather_qmm_chain(const void* x, const uint32_t* wq1, const void* scales1, const void* biases1,
+                                      const uint32_t* wq2, const void* scales2, const void* biases2,
+                                      const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* y, int dtype,
+                                      int64_t x_batch, int64_t E, int64_t M, int64_t N1, int64_t K1, int64_t N2,
+                                      int group_size, int bits, void* ws, size_t ws_bytes, void* stream) {
+  if (!valid_group(group_size) || !valid_bits(bits))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_chain] group size must be 32, 64 or 128 and bits 2, 3, 4, 5, 6 or 8");
+  if (n_idx < 0 || x_batch < 0 || E < 1 || M < 0 || N1 < 0 || K1 < 0 || N2 < 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_chain] negative dimension.");
+  if (K1 % group_size != 0 || (K1 * bits) % 32 != 0 || N1 % group_size != 0 || (N1 * bits) % 32 != 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_chain] The shapes of the weight and scales are incompatible based on bits and group_size");
+  if (n_idx == 0 || M == 0 || N2 == 0) return B200Q_OK;
+  if (!x || !wq1 || !scales1 || !biases1 || !wq2 || !scales2 || !biases2 || !lhs_idx || !rhs_idx || !y)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_chain] null pointer");
+  const bool aligned = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wq1) | reinterpret_cast<uintptr_t>(wq2) |
+                          reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(y)) & 15);
+  if (!aligned || !fast_supported(dtype, n_idx, x_batch, E, M, N1, K1, group_size, bits, 1) ||
+      !fast_supported(dtype, n_idx, n_idx, E, M, N2, N1, group_size, bits, 1))
+    return fail(B200Q_ERR_UNSUPPORTED, "[gather_qmm_chain] only bfloat16 with K and the inner width multiples of 128 (two b200q_gather_qmm calls cover the rest)");
+  const size_t need = b200q_gather_qmm_chain_workspace_bytes(n_idx, E, M, N1, K1);
+  if (!ws || ws_bytes < need)
+    return fail(B200Q_ERR_WORKSPACE, "[gather_qmm_chain] workspace of %zu bytes required, %zu given", need, ws_bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* status = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes);
+  const FastLayout L = fast_layout(n_idx, E, M, K1);
+  char* base = static_cast<char*>(ws);
+  Header* hdr = reinterpret_cast<Header*>(base + L.hdr);
+  int* sorted = reinterpret_cast<int*>(base + L.sorted);
+  int* dst = reinterpret_cast<int*>(base + L.dst);
+  MTileRec* mt = reinterpret_cast<MTileRec*>(base + L.mtiles);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + L.xs);
+  __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(base + L.total - 256);   // after the gathered rows
+  gather_sort_kernel<<<1, 1024, 0, st>>>(lhs_idx, rhs_idx, (int)n_idx, (uint32_t)x_batch, (uint32_t)E, 0u, (uint32_t)E, (int)M,
+                                         L.nt, hdr, sorted, mt, y, (size_t)M * N2 * 2, status);
+  B200Q_LAUNCH_OK("gather_sort_kernel");
+  gather_rows_kernel<<<(unsigned)L.n_rows, 256, 0, st>>>((const __nv_bfloat16*)x, lhs_idx, hdr, sorted, (int)M, (int)K1, xs, dst);
+  B200Q_LAUNCH_OK("gather_rows_kernel");
+  GroupedArgs g{};
+  g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles;
+  g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E;
+  g.group = group_size; g.bits = bits; g.nt = L.nt; g.status = status;
+  // first product: rows stay in expert order (no scatter), result = activation of the second
+  g.x_sorted = xs; g.wq = wq1; g.scales = scales1; g.biases = biases1; g.y = h; g.dst_row = nullptr; g.N = N1; g.K = K1;
+  if (int rc = qmm_tc_grouped(g, st)) return rc;
+  // second product: same tile table, rows scattered to the positions of their index pairs
+  g.x_sorted = h; g.wq = wq2; g.scales = scales2; g.biases = biases2; g.y = y; g.dst_row = dst; g.N = N2; g.K = N1;
+  return qmm_tc_grouped(g, st);
+}

@@ -323,3 +323,45 @@ def qmm_kernel_name(dtype: torch.dtype, M: int, N: int, K: int, group_size: int 
                     transpose: bool = True, batch: int = 1) -> str:
     """Which kernel family quantized_matmul launches for this problem."""
     return _lib.load().b200q_qmm_kernel_name(_DT[dtype], batch, M, N, K, group_size, bits, int(transpose)).decode()
+
+
+def gather_qmm_chain(x: torch.Tensor, w1: torch.Tensor, scales1: torch.Tensor, biases1: torch.Tensor,
+                     w2: torch.Tensor, scales2: torch.Tensor, biases2: torch.Tensor,
+                     rhs_indices: torch.Tensor, lhs_indices: Optional[torch.Tensor] = None,
+                     group_size: Optional[int] = None, bits: Optional[int] = None) -> torch.Tensor:
+    """gather_qmm(gather_qmm(x, w1, ...), w2, ...) over the same index pairs with one sort by expert
+    (the reference composes the two calls, benchmarks/python/gather_qmm_bench.py:52-63).
+    x [B, M, K1] bf16; w1 [E, N1, K1*bits/32]; w2 [E, N2, N1*bits/32]; out: idx_shape + [M, N2]."""
+    group_size, bits = _mode_params("affine", group_size, bits, "gather_qmm_chain")
+    _validate_quantized_input("gather_qmm_chain", w1, scales1, group_size, bits, biases1)
+    _validate_quantized_input("gather_qmm_chain", w2, scales2, group_size, bits, biases2)
+    if x.dtype != torch.bfloat16 or x.ndim < 2:
+        raise ValueError("[gather_qmm_chain] x must be bfloat16 with at least two dimensions")
+    dev = _require_cuda("gather_qmm_chain", x, w1, scales1, biases1, w2, scales2, biases2)
+    M, K1 = x.shape[-2], x.shape[-1]
+    N1, N2 = w1.shape[-2], w2.shape[-2]
+    if w1.shape[-1] * 32 // bits != K1 or w2.shape[-1] * 32 // bits != N1 or w1.shape[:-2] != w2.shape[:-2]:
+        raise ValueError("[gather_qmm_chain] w1 must map K1 -> N1 and w2 N1 -> N2 for the same experts")
+    x_batch = x.numel() // max(M * K1, 1)
+    E = w1.numel() // max(w1.shape[-1] * N1, 1)
+    rhs = rhs_indices.to(device=dev, dtype=torch.int64)
+    lhs = (torch.arange(x_batch, device=dev).reshape(tuple(x.shape[:-2])) if lhs_indices is None
+           else lhs_indices.to(device=dev, dtype=torch.int64))
+    lhs, rhs = torch.broadcast_tensors(lhs, rhs)
+    idx_shape = tuple(lhs.shape)
+    lhs32, rhs32 = lhs.contiguous().reshape(-1).to(torch.int32), rhs.contiguous().reshape(-1).to(torch.int32)
+    n_idx = lhs32.numel()
+    x = x.contiguous()
+    c = lambda t: t.to(torch.bfloat16).contiguous()
+    scales1, biases1, scales2, biases2 = c(scales1), c(biases1), c(scales2), c(biases2)
+    w1, w2 = w1.contiguous(), w2.contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        y = torch.empty(idx_shape + (M, N2), dtype=torch.bfloat16, device=dev)
+        need = lib.b200q_gather_qmm_chain_workspace_bytes(n_idx, E, M, N1, K1)
+        ws = _workspaces.get(dev, need, "gather")
+        rc = lib.b200q_gather_qmm_chain(_ptr(x), _ptr(w1), _ptr(scales1), _ptr(biases1), _ptr(w2), _ptr(scales2),
+                                        _ptr(biases2), _ptr(lhs32), _ptr(rhs32), n_idx, _ptr(y), _lib.BF16, x_batch, E, M,
+                                        N1, K1, N2, group_size, bits, _ptr(ws), ws.numel(), _stream(x))
+    _lib.check(rc)
+    return y

@@ -172,3 +172,29 @@ def test_gather_then_decode_on_one_stream():
         ref = O.qmm_f32_from(x[:3, 0], wq[1], s[1], b[1], dtype, transpose=True, group_size=g, bits=4)
         ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), ref)
         assert ok, rel
+
+
+@pytest.mark.parametrize("E,tokens,topk,K1,N1,N2", [(8, 96, 2, 512, 384, 256), (4, 33, 4, 1024, 1024, 128)])
+def test_gather_chain_vs_two_calls_and_oracle(E, tokens, topk, K1, N1, N2):
+    """Two chained gather_qmm with one sort: identical to calling gather_qmm twice (the kernels and
+    the rounding of the intermediate are the same) and close to the oracle."""
+    g, dtype = 64, "bf16"
+    wq1, s1, b1 = O.quantize(make_w(50, (E, N1, K1), dtype), g, 4, dtype)
+    wq2, s2, b2 = O.quantize(make_w(51, (E, N2, N1), dtype), g, 4, dtype)
+    x = make_x(52, (tokens, 1, K1), dtype)
+    rng = np.random.default_rng(9)
+    rhs = rng.integers(0, E, size=(tokens, topk)).astype(np.int64)
+    t = lambda a: to_torch(a, dtype)
+    args1 = (u32_to_torch(wq1), t(s1), t(b1))
+    args2 = (u32_to_torch(wq2), t(s2), t(b2))
+    lhs = torch.arange(tokens).reshape(tokens, 1).expand(tokens, topk)
+    y = mb.gather_qmm_chain(t(x), *args1, *args2, rhs_indices=torch.from_numpy(rhs), lhs_indices=lhs)
+    assert tuple(y.shape) == (tokens, topk, 1, N2)
+    h = mb.gather_qmm(t(x), *args1, lhs_indices=lhs, rhs_indices=torch.from_numpy(rhs))           # [tokens, topk, 1, N1]
+    y2 = mb.gather_qmm(h.reshape(tokens * topk, 1, N1), *args2, rhs_indices=torch.from_numpy(rhs.reshape(-1)))
+    assert torch.equal(y.reshape(-1, N2).view(torch.int16), y2.reshape(-1, N2).view(torch.int16))
+    hq = from_torch(h.reshape(tokens * topk, 1, N1).contiguous())
+    ref = O.gather_qmm(O.to_f32(hq, dtype), wq2, O.to_f32(s2, dtype), O.to_f32(b2, dtype),
+                       np.arange(tokens * topk, dtype=np.uint32), rhs.reshape(-1).astype(np.uint32), True, g, 4, "f32")
+    ok, rel = qmm_close(O.to_f32(from_torch(y.contiguous()), dtype).reshape(ref.shape), ref)
+    assert ok, rel
