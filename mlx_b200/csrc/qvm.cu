@@ -92,36 +92,50 @@ qvm_kernel(const T* __restrict__ x, const uint32_t* __restrict__ wq, const T* __
     const int gcol = n0 / group;
     const uint32_t* wp = wq + (int64_t)(k0 + warp) * row_words + (int64_t)lane * NW;
     wp += (int64_t)blockIdx.x * (kQvmCols * BITS / 32);
-    for (int k = k0 + warp; k < k1; k += kQvmWarps, wp += (int64_t)kQvmWarps * row_words) {
-      uint32_t w[NW];
-      if constexpr (NW == 4) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(wp));
-        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-      } else if constexpr (NW == 2) {
-        const uint2 v = __ldg(reinterpret_cast<const uint2*>(wp));
-        w[0] = v.x; w[1] = v.y;
-      } else {
-        w[0] = __ldg(wp);
+    // Two rows per iteration: both rows' loads are issued before either is used.
+    constexpr int RB = 2;
+    for (int k = k0 + warp; k < k1; k += RB * kQvmWarps, wp += (int64_t)RB * kQvmWarps * row_words) {
+      uint32_t w[RB][NW];
+      float sv[RB], bv[RB];
+#pragma unroll
+      for (int u = 0; u < RB; ++u) {
+        const int ku = k + u * kQvmWarps;
+        const bool on = ku < k1;
+        const uint32_t* wpu = wp + (int64_t)u * kQvmWarps * row_words;
+        if constexpr (NW == 4) {
+          const uint4 v = on ? __ldg(reinterpret_cast<const uint4*>(wpu)) : make_uint4(0, 0, 0, 0);
+          w[u][0] = v.x; w[u][1] = v.y; w[u][2] = v.z; w[u][3] = v.w;
+        } else if constexpr (NW == 2) {
+          const uint2 v = on ? __ldg(reinterpret_cast<const uint2*>(wpu)) : make_uint2(0, 0);
+          w[u][0] = v.x; w[u][1] = v.y;
+        } else {
+          w[u][0] = on ? __ldg(wpu) : 0u;
+        }
+        sv[u] = on ? Elem<T>::to_float(scales[(int64_t)ku * row_groups + gcol]) : 0.0f;
+        bv[u] = on ? Elem<T>::to_float(biases[(int64_t)ku * row_groups + gcol]) : 0.0f;
       }
-      const float s = Elem<T>::to_float(scales[(int64_t)k * row_groups + gcol]);
-      const float b = Elem<T>::to_float(biases[(int64_t)k * row_groups + gcol]);
-      float q[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        constexpr int per_word = 32 / BITS;
-        const uint32_t word = w[j / per_word];
-        const int sh = (j % per_word) * BITS;          // field at bits [sh, sh + BITS)
-        const uint32_t moved = sh >= kPos ? (word >> (sh - kPos)) : (word << (kPos - sh));
-        q[j] = __uint_as_float((moved & kMask) | kMagic);
-      }
+      for (int u = 0; u < RB; ++u) {
+        const int ku = k + u * kQvmWarps;
+        const int kx = ku < k1 ? ku - k0 : 0;   // rows past the slab have s = b = 0: they add nothing
+        float q[16];
 #pragma unroll
-      for (int m = 0; m < MM; ++m) {
-        const float xv = xs[m * slab + (k - k0)];
-        const float xsc = xv * s;
-        sum_xs[m] += xsc;
-        sum_xb[m] = fmaf(xv, b, sum_xb[m]);
+        for (int j = 0; j < 16; ++j) {
+          constexpr int per_word = 32 / BITS;
+          const uint32_t word = w[u][j / per_word];
+          const int sh = (j % per_word) * BITS;          // field at bits [sh, sh + BITS)
+          const uint32_t moved = sh >= kPos ? (word >> (sh - kPos)) : (word << (kPos - sh));
+          q[j] = __uint_as_float((moved & kMask) | kMagic);
+        }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[m][j] = fmaf(xsc, q[j], acc[m][j]);
+        for (int m = 0; m < MM; ++m) {
+          const float xv = xs[m * slab + kx];
+          const float xsc = xv * sv[u];
+          sum_xs[m] += xsc;
+          sum_xb[m] = fmaf(xv, bv[u], sum_xb[m]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[m][j] = fmaf(xsc, q[j], acc[m][j]);
+        }
       }
     }
 #pragma unroll
