@@ -23,6 +23,8 @@
 //
 // Scratch (caller-provided workspace, zero on first use, self-cleaning afterwards):
 //   [ counters: ceil(N/16) x u32 | fp32 partial tiles: ceil(N/16)*16 rows x 16 tokens ]
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -196,6 +198,8 @@ qmv_mma_kernel(const QmvParams p) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
                  : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
   }
+  // let the next kernel of the stream start as soon as SMs free up (it waits before it reads x)
+  asm volatile("griddepcontrol.launch_dependents;");
   const long long T = p.total_steps;  // < 2^31 (checked on the host)
   const int G = gridDim.x;
   const int ksteps = p.ksteps;
@@ -247,6 +251,11 @@ qmv_mma_kernel(const QmvParams p) {
   for (int d = 0; d < kPipe; ++d)
     if (s0 + d < s1) issue(d);
 
+  // Programmatic dependent launch: the weight loads above read constants, so they may run while
+  // the previous kernel of the stream (e.g. the previous decode step) is still finishing.
+  // Everything that kernel may produce (x) or still use (y, the workspace) is touched only after
+  // this point.  Without the launch attribute the instruction returns at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- stage x in B-fragment order; zero the tile buffer -------------------------
   {
     constexpr int U = 8;  // loads in flight per thread
@@ -477,12 +486,36 @@ QmvPlan make_plan(const QmmArgs& a) {
 size_t counters_bytes(int64_t N) { return (size_t)(((N + 15) / 16 * 4 + 255) / 256 * 256); }
 size_t partial_bytes(int64_t N) { return (size_t)((N + 31) / 32 * 32) * 16 * 4; }
 
+// B200Q_PDL=0 turns programmatic dependent launch off (plain stream order).
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <int BITS>
 int launch(const QmvPlan& pl, cudaStream_t st) {
   auto go = [&](auto kern) -> int {
     if (pl.smem > 48 * 1024)
       B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-    kern<<<pl.grid, kThreads, pl.smem, st>>>(pl.prm);
+    if (pdl_enabled()) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(pl.grid);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = pl.smem;
+      cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, pl.prm));
+    } else {
+      kern<<<pl.grid, kThreads, pl.smem, st>>>(pl.prm);
+    }
     B200Q_LAUNCH_OK("qmv_mma_kernel");
     return B200Q_OK;
   };
