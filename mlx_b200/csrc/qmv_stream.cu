@@ -33,6 +33,7 @@
 //   [ counters: one u32 per row block | slots: kMaxCtas x 2 x 128 rows x 16 tokens fp32 ]
 #include <cuda.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -255,6 +256,7 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
                  : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
   }
+  asm volatile("griddepcontrol.launch_dependents;");
   if (tid == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   if (tid == 64) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
   if (tid == 0) {
@@ -314,13 +316,16 @@ qmv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     //      (warp i, box i).  Then every 8-k octet is permuted in place to
     //      (x0,x4),(x1,x5),(x2,x6),(x3,x7), the order the unpacked weight pairs come in.
     {
+      // Only the first box is requested together with x: a deeper prefetch from every SM at once
+      // would put megabytes of weight requests in front of the few kilobytes everything waits for.
+      // The box is a constant: it may be requested while the previous kernel of the stream is
+      // still running (programmatic dependent launch); x, y and the workspace only after the wait.
+      if (warp == 0 && n_boxes > 0) issue_box(0u, rb_first, kc_first);
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       if (tid == 0) {
         mbar_expect_tx(smem_u32(&bars->xbar), (uint32_t)(p.K * TS * 2));
         tma_load_3d(xs_u, &map_x, 0, 0, 0, smem_u32(&bars->xbar));
       }
-      // Only the first box is requested together with x: a deeper prefetch from every SM at once
-      // would put megabytes of weight requests in front of the few kilobytes everything waits for.
-      if (warp == 0 && n_boxes > 0) issue_box(0u, rb_first, kc_first);
       if (warp == 0) QS_MARK(10);
       for (int i = ctid; i < 2 * kRows * TOK; i += kWarps * 32) tile[i] = 0.0f;
 #ifdef B200Q_PROFILE
@@ -701,7 +706,25 @@ int launch(const QmmArgs& a, const CUtensorMap& map_w, EncodeFn enc, SParams& p,
   const Layout L = make_layout<MT, GROUP>((int)a.K, p.stages, p.toks);
   cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<MT, GROUP, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
   if (e != cudaSuccess) return fail(B200Q_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-  qmv_stream_kernel<MT, GROUP, NG><<<grid, kThreads, L.total, st>>>(map_w, map_x, p);
+  {
+    const char* e = getenv("B200Q_PDL");
+    if (e && e[0] == '0') {
+      qmv_stream_kernel<MT, GROUP, NG><<<grid, kThreads, L.total, st>>>(map_w, map_x, p);
+    } else {
+      // programmatic dependent launch: see the griddepcontrol instructions in the kernel
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(grid);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = L.total;
+      cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, qmv_stream_kernel<MT, GROUP, NG>, map_w, map_x, p));
+    }
+  }
   B200Q_LAUNCH_OK("qmv_stream_kernel");
   return B200Q_OK;
 }
