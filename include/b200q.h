@@ -134,7 +134,8 @@ int b200q_read_status(void* ws, size_t ws_bytes, void* stream, uint32_t status[4
 /*
  * Host-buffer form of b200q_qmm for callers that hold activations in host memory:
  * copies x (host, ideally pinned) to x_dev, runs the operator, copies y_dev back to
- * y_host, all on `stream`, and returns without synchronising.  Weights, scales and
+ * y_host, all on `stream`, and returns without synchronising.  When y_host is pinned and the
+ * result is at most 4 MiB the kernel writes it to host memory itself and y_dev is not used.  Weights, scales and
  * biases are device resident.  x_dev / y_dev are caller-provided device staging
  * buffers of M*K and M*N elements.
  */

@@ -351,6 +351,23 @@ extern "C" int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* w
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t es = dtype_size(dtype);
   B200Q_CUDA_OK(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * es, cudaMemcpyHostToDevice, st));
+  // A small result in pinned host memory is written by the kernel itself (the stores go out over
+  // PCIe as the tiles finish), which saves the separate device-to-host copy and its launch gap.
+  // B200Q_HOST_DIRECT=0 keeps the staged copy.
+  static int direct = -1;
+  if (direct < 0) {
+    const char* e = getenv("B200Q_HOST_DIRECT");
+    direct = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (direct && (size_t)M * N * es <= (4u << 20)) {
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer != nullptr) {
+      a.y = attr.devicePointer;
+      return run_qmm(a, st);
+    }
+    cudaGetLastError();   // an unregistered host pointer is not an error here
+  }
   if (int rc = run_qmm(a, st)) return rc;
   B200Q_CUDA_OK(cudaMemcpyAsync(y_host, y_dev, (size_t)M * N * es, cudaMemcpyDeviceToHost, st));
   return B200Q_OK;

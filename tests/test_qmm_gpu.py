@@ -240,3 +240,35 @@ def test_qvm_then_transposed_decode_share_workspace():
     for _ in range(2):
         run_case("bf16", 2, 4096, 2048, 64, 4, transpose=False, seed=11, expect_kernel=("qvm",))
         run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_mma", "qmv_stream"))
+
+
+# ---- host-buffer entry point -------------------------------------------------------------------
+@pytest.mark.parametrize("pinned", (True, False))
+@pytest.mark.parametrize("M", (16, 64))
+def test_qmm_host_buffers(pinned, M):
+    """b200q_qmm_host with pinned (result written by the kernel straight to host memory when small)
+    and pageable (staged copy) host buffers gives the same result as the device call."""
+    import ctypes
+    from mlx_b200 import _lib
+    lib = _lib.load()
+    N, K, g = 1024, 512, 64
+    wq, s, b = O.quantize(make_w(3, (N, K), "bf16"), g, 4, "bf16")
+    x = make_x(4, (M, K), "bf16")
+    ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
+    wq_t, s_t, b_t = u32_to_torch(wq), to_torch(s, "bf16"), to_torch(b, "bf16")
+    x_host = to_torch(x, "bf16").cpu()
+    y_host = torch.zeros(M, N, dtype=torch.bfloat16)
+    if pinned:
+        x_host, y_host = x_host.pin_memory(), y_host.pin_memory()
+    x_dev = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    y_dev = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    need = max(int(lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, M, N, K, g, 4, 1)), 256)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    for _ in range(2):
+        rc = lib.b200q_qmm_host(P(x_host), P(x_dev), P(wq_t), P(s_t), P(b_t), P(y_dev), P(y_host), _lib.BF16, M, N, K, g, 4, 1,
+                                P(ws), ws.numel(), None)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+    ok, rel = qmm_close(O.to_f32(y_host.view(torch.int16).numpy().view(np.uint16), "bf16"), ref)
+    assert ok, rel
