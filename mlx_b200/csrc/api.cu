@@ -208,6 +208,13 @@ __global__ void peer_wait_kernel(const uint32_t* flag, const uint32_t* epoch, ui
     __nanosleep(200);
   }
 }
+// Copies n16 16-byte pieces from (mapped, pinned) host memory to device memory.  The next kernel
+// of the stream may start early: it waits for this grid before it reads the destination.
+__global__ void __launch_bounds__(256) host_fetch_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t n16) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n16) dst[i] = src[i];
+}
 // y[i] = sum over the n_slots partial results slots[r * stride + i], added in fp32 in slot order,
 // rounded once to T.  Eight elements per thread.
 template <typename T>
@@ -339,6 +346,18 @@ extern "C" int b200q_read_status(void* ws, size_t ws_bytes, void* stream, uint32
   return B200Q_OK;
 }
 
+namespace {
+// B200Q_HOST_DIRECT=0: b200q_qmm_host always uses staged copies
+bool host_direct() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_HOST_DIRECT");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+}  // namespace
+
 extern "C" int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* wq, const void* scales,
                               const void* biases, void* y_dev, void* y_host, int dtype, int64_t M, int64_t N,
                               int64_t K, int group_size, int bits, int transpose, void* ws, size_t ws_bytes,
@@ -350,16 +369,29 @@ extern "C" int b200q_qmm_host(const void* x_host, void* x_dev, const uint32_t* w
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null host/staging pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t es = dtype_size(dtype);
-  B200Q_CUDA_OK(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * es, cudaMemcpyHostToDevice, st));
+  // Small activations in pinned host memory are fetched by a copy kernel instead of a memcpy: the
+  // decode kernels start under programmatic dependent launch, so their weight loads overlap the
+  // PCIe read instead of queueing behind it.
+  bool staged_x = false;
+  if (host_direct() && (size_t)M * K * es <= (1u << 20) && ((size_t)M * K * es) % 16 == 0 &&
+      !(reinterpret_cast<uintptr_t>(x_dev) & 15)) {
+    cudaPointerAttributes xa{};
+    if (cudaPointerGetAttributes(&xa, x_host) == cudaSuccess && xa.type == cudaMemoryTypeHost && xa.devicePointer != nullptr &&
+        !(reinterpret_cast<uintptr_t>(xa.devicePointer) & 15)) {
+      const int64_t n16 = (int64_t)((size_t)M * K * es / 16);
+      const unsigned grid = (unsigned)((n16 + 255) / 256);
+      peer::host_fetch_kernel<<<grid, 256, 0, st>>>(static_cast<const uint4*>(xa.devicePointer), static_cast<uint4*>(x_dev), n16);
+      B200Q_LAUNCH_OK("host_fetch_kernel");
+      staged_x = true;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  if (!staged_x) B200Q_CUDA_OK(cudaMemcpyAsync(x_dev, x_host, (size_t)M * K * es, cudaMemcpyHostToDevice, st));
   // A small result in pinned host memory is written by the kernel itself (the stores go out over
   // PCIe as the tiles finish), which saves the separate device-to-host copy and its launch gap.
   // B200Q_HOST_DIRECT=0 keeps the staged copy.
-  static int direct = -1;
-  if (direct < 0) {
-    const char* e = getenv("B200Q_HOST_DIRECT");
-    direct = (e && e[0] == '0') ? 0 : 1;
-  }
-  if (direct && (size_t)M * N * es <= (4u << 20)) {
+  if (host_direct() && (size_t)M * N * es <= (4u << 20)) {
     cudaPointerAttributes attr{};
     if (cudaPointerGetAttributes(&attr, y_host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
         attr.devicePointer != nullptr) {
