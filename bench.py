@@ -233,7 +233,13 @@ def main():
     fused = world > 1 and args.gather == "fused"
     if fused:
         from mlx_b200.distributed import PeerOutput, QuantizedAllToShardedLinear, sharded_matmul_allgather
-        peer_out = PeerOutput(M_DEC, N_DEC)
+        try:
+            peer_out = PeerOutput(M_DEC, N_DEC)
+        except RuntimeError as e:   # raised on every rank together: fall back to the collective
+            if rank == 0:
+                print(f"bench: fused gather unavailable ({e}); using NCCL", file=sys.stderr)
+            fused = False
+    if fused:
         layers = [QuantizedAllToShardedLinear(q, s, b, GROUP, BITS, rank=rank, world=world, already_sharded=True)
                   for (q, s, b) in weights]
 

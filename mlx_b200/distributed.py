@@ -133,20 +133,43 @@ class PeerOutput:
         self.m_max, self.n_total = m_max, n_total
         self.buf_bytes = (m_max * n_total * 2 + 255) // 256 * 256
         total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word and (at +128) the epoch
+        # Every rank walks the same sequence of collectives even when a local step fails; the failure
+        # is agreed on at the end, so that all ranks raise together instead of some of them hanging.
+        err = None
         ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
-        _lib.check(self.lib.b200q_ipc_alloc(total, ctypes.byref(ptr), handle))
-        self._own = ptr.value
+        self._own = None
+        try:
+            _lib.check(self.lib.b200q_ipc_alloc(total, ctypes.byref(ptr), handle))
+            self._own = ptr.value
+        except Exception as e:  # noqa: BLE001
+            err = e
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle), group=group)
+        dist.all_gather_object(handles, bytes(handle) if err is None else None, group=group)
         self.base = []
-        for q in range(self.world):
-            if q == self.rank:
-                self.base.append(self._own)
-            else:
-                p = ctypes.c_void_p()
-                h = (ctypes.c_ubyte * 64).from_buffer_copy(handles[q])
-                _lib.check(self.lib.b200q_ipc_open(h, ctypes.byref(p)))
-                self.base.append(p.value)
+        if err is None and all(h is not None for h in handles):
+            try:
+                for q in range(self.world):
+                    if q == self.rank:
+                        self.base.append(self._own)
+                    else:
+                        p = ctypes.c_void_p()
+                        h = (ctypes.c_ubyte * 64).from_buffer_copy(handles[q])
+                        _lib.check(self.lib.b200q_ipc_open(h, ctypes.byref(p)))
+                        self.base.append(p.value)
+            except Exception as e:  # noqa: BLE001
+                err = e
+        elif err is None:
+            err = RuntimeError("another rank could not allocate its buffer")
+        oks = [None] * self.world
+        dist.all_gather_object(oks, err is None, group=group)
+        if not all(oks):
+            for q, b in enumerate(self.base):
+                if q != self.rank:
+                    self.lib.b200q_ipc_close(ctypes.c_void_p(b))
+            if self._own is not None:
+                self.lib.b200q_ipc_free(ctypes.c_void_p(self._own))
+                self._own = None
+            raise RuntimeError(f"[PeerOutput] peer-mapped output buffers are not available on every rank: {err}")
         self.flag = [b + self.N_BUF * self.buf_bytes for b in self.base]
         self.epoch = self._own + self.N_BUF * self.buf_bytes + 128
         self.step = 0
