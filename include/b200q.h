@@ -87,6 +87,17 @@ int b200q_dequantize(const uint32_t* wq, const void* scales, const void* biases,
                      int64_t rows, int64_t K, int group_size, int bits, void* out, void* stream);
 
 /*
+ * Quantized embedding look-up: out[i, :] = dequantize(row ids[i] of the packed matrix), the fused form
+ * of QuantizedEmbedding.__call__ (python/mlx/nn/layers/quantized.py:149-158), which indexes the
+ * three arrays by ids and then dequantizes.
+ *   wq [rows, K*bits/32], scales/biases [rows, K/g] dtype, ids uint32 [n_ids], out [n_ids, K] dtype.
+ * An id outside [0, rows) gives a row of zeros and reads nothing (the reference leaves it undefined).
+ */
+int b200q_dequantize_rows(const uint32_t* wq, const void* scales, const void* biases, const uint32_t* ids,
+                          int64_t n_ids, int dtype, int64_t rows, int64_t K, int group_size, int bits,
+                          void* out, void* stream);
+
+/*
  * y[b] = x[b] * dequant(w[b])^T   (transpose != 0;  wq [N, K*bits/32], scales [N, K/g])
  * y[b] = x[b] * dequant(w[b])     (transpose == 0;  wq [K, N*bits/32], scales [K, N/g])
  *   x [batch, M, K], y [batch, M, N]  dtype, row-contiguous

@@ -26,6 +26,7 @@ SIGNATURES = {
     "b200q_last_error": (ctypes.c_char_p, []),
     "b200q_quantize": (_i, [_vp, _i, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp]),
     "b200q_dequantize": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _i, _i, _vp, _vp]),
+    "b200q_dequantize_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i64, _i, _i, _vp, _vp]),
     "b200q_qmm_workspace_bytes": (_sz, [_i, _i64, _i64, _i64, _i64, _i, _i, _i]),
     "b200q_qmm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i, _i, _i, _i64, _vp, _sz, _vp]),
     "b200q_gather_qmm_workspace_bytes": (_sz, [_i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i]),

@@ -218,6 +218,64 @@ int launch_dequantize(const uint32_t* wq, const T* s, const T* b, int64_t n_elem
   return B200Q_OK;
 }
 
+// Rows of the packed matrix chosen by `ids` (an embedding look-up): out[i, :] = dequantize(row ids[i]).
+// An id outside [0, rows) gives a row of zeros; nothing is read for it.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+dequantize_rows_kernel(const uint32_t* __restrict__ wq, const T* __restrict__ scales,
+                       const T* __restrict__ biases, const uint32_t* __restrict__ ids, T* __restrict__ out,
+                       int64_t rows, int chunks_per_row, int group_shift, int64_t n_words) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= chunks_per_row) return;
+  const int64_t i = blockIdx.y;
+  const uint32_t id = __ldg(ids + i);
+  T* dst = out + (i * chunks_per_row + c) * 8;
+  float v[8];
+  if ((int64_t)id >= rows) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = 0.f;
+    store8(dst, v);
+    return;
+  }
+  const int64_t cg = (int64_t)id * chunks_per_row + c;  // chunk index in the whole matrix
+  const int64_t byte = cg * BITS;
+  const int64_t w0 = byte >> 2;
+  const int sh = (int)(byte & 3) * 8;
+  uint32_t a = __ldg(wq + w0);
+  uint32_t b = (w0 + 1 < n_words) ? __ldg(wq + w0 + 1) : 0u;
+  uint64_t bitsv = ((uint64_t)(b >> sh) << 32) | __funnelshift_r(a, b, sh);
+  const int64_t g = cg >> group_shift;
+  const float s = Elem<T>::to_float(scales[g]);
+  const float bs = Elem<T>::to_float(biases[g]);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float q = (float)(uint32_t)((bitsv >> (k * BITS)) & ((1u << BITS) - 1u));
+    float t = Elem<T>::to_float(Elem<T>::from_float(__fmul_rn(q, s)));
+    v[k] = __fadd_rn(t, bs);
+  }
+  store8(dst, v);
+}
+
+template <typename T>
+int launch_dequantize_rows(const uint32_t* wq, const T* s, const T* b, const uint32_t* ids, int64_t n_ids,
+                           int64_t rows, int64_t K, int group, int bits, T* out, cudaStream_t st) {
+  const int cpr = (int)(K / 8);
+  const int gshift = group == 32 ? 2 : (group == 64 ? 3 : 4);
+  const int64_t n_words = rows * K * bits / 32;
+  bool done = false;
+  for (int64_t i0 = 0; i0 < n_ids; i0 += 65535) {   // gridDim.y limit
+    const unsigned ny = (unsigned)((n_ids - i0) < 65535 ? (n_ids - i0) : 65535);
+    dim3 grid((unsigned)((cpr + 255) / 256), ny);
+    B200Q_DISPATCH_BITS(bits, BITS, {
+      dequantize_rows_kernel<T, BITS><<<grid, 256, 0, st>>>(wq, s, b, ids + i0, out + i0 * K, rows, cpr, gshift, n_words);
+      done = true;
+    });
+    if (!done) return fail(B200Q_ERR_INVALID_ARGUMENT, "[dequantize_rows] unsupported bits %d", bits);
+    B200Q_LAUNCH_OK("dequantize_rows_kernel");
+  }
+  return B200Q_OK;
+}
+
 int check_quant_args(const char* tag, int dtype, int64_t rows, int64_t K, int group, int bits) {
   if (dtype != B200Q_F32 && dtype != B200Q_F16 && dtype != B200Q_BF16)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[%s] Only real floating types are supported (dtype code %d).", tag, dtype);
@@ -279,5 +337,30 @@ extern "C" int b200q_dequantize(const uint32_t* wq, const void* scales, const vo
     default:
       return launch_dequantize<__nv_bfloat16>(wq, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)biases, n,
                                               group_size, bits, (__nv_bfloat16*)out, st);
+  }
+}
+
+extern "C" int b200q_dequantize_rows(const uint32_t* wq, const void* scales, const void* biases, const uint32_t* ids,
+                                     int64_t n_ids, int dtype, int64_t rows, int64_t K, int group_size, int bits,
+                                     void* out, void* stream) {
+  if (int rc = check_quant_args("dequantize_rows", dtype, rows, K, group_size, bits)) return rc;
+  if (n_ids < 0) return fail(B200Q_ERR_INVALID_ARGUMENT, "[dequantize_rows] negative number of ids (%lld).", (long long)n_ids);
+  if (K / 8 > INT32_MAX) return fail(B200Q_ERR_UNSUPPORTED, "[dequantize_rows] row too long.");
+  if (n_ids == 0 || K == 0) return B200Q_OK;
+  if (!out || !ids) return fail(B200Q_ERR_INVALID_ARGUMENT, "[dequantize_rows] null pointer");
+  if (rows > 0 && (!wq || !scales || !biases)) return fail(B200Q_ERR_INVALID_ARGUMENT, "[dequantize_rows] null pointer");
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(wq) & 3))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[dequantize_rows] out must be 16-byte aligned and wq 4-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case B200Q_F32:
+      return launch_dequantize_rows<float>(wq, (const float*)scales, (const float*)biases, ids, n_ids, rows, K, group_size,
+                                           bits, (float*)out, st);
+    case B200Q_F16:
+      return launch_dequantize_rows<__half>(wq, (const __half*)scales, (const __half*)biases, ids, n_ids, rows, K,
+                                            group_size, bits, (__half*)out, st);
+    default:
+      return launch_dequantize_rows<__nv_bfloat16>(wq, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)biases, ids,
+                                                   n_ids, rows, K, group_size, bits, (__nv_bfloat16*)out, st);
   }
 }

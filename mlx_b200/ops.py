@@ -209,6 +209,44 @@ def dequantize(w: torch.Tensor, scales: torch.Tensor, biases: Optional[torch.Ten
     return out if out.dtype == out_type else out.to(out_type)
 
 
+def quantized_embedding(ids: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+                        group_size: Optional[int] = None, bits: Optional[int] = None,
+                        mode: str = "affine") -> torch.Tensor:
+    """QuantizedEmbedding.__call__ (python/mlx/nn/layers/quantized.py:149-158):
+    dequantize(w[ids], scales[ids], biases[ids]) as one kernel.  ids: any integer tensor;
+    out: ids.shape + [K] in the dtype of scales."""
+    group_size, bits = _mode_params(mode, group_size, bits, "quantized_embedding")
+    _validate_mode_with_type("quantized_embedding", scales, biases, None)
+    if w.dtype != torch.uint32:
+        raise ValueError("[quantized_embedding] The matrix should be given as a uint32")
+    if w.ndim != 2 or scales.ndim != 2 or biases.shape != scales.shape or scales.shape[0] != w.shape[0]:
+        raise ValueError("[quantized_embedding] Shape of scales and biases does not match the matrix")
+    K = w.shape[-1] * 32 // bits
+    if K != scales.shape[-1] * group_size:
+        raise ValueError(
+            "[quantized_embedding] Shape of scales and biases does not match the matrix given the quantization "
+            f"parameters. Provided matrix of shape {tuple(w.shape)} and scales/biases of shape "
+            f"{tuple(scales.shape)} with group_size={group_size} and bits={bits}."
+        )
+    if ids.dtype.is_floating_point or ids.dtype == torch.bool:
+        raise ValueError("[quantized_embedding] ids must be integral.")
+    if scales.dtype not in _DT or scales.dtype != biases.dtype:
+        ct = torch.promote_types(scales.dtype, biases.dtype)
+        scales, biases = scales.to(ct), biases.to(ct)
+    dev = _require_cuda("quantized_embedding", w, scales, biases)
+    w, scales, biases = w.contiguous(), scales.contiguous(), biases.contiguous()
+    ids64 = ids.to(device=dev, dtype=torch.int64).contiguous().reshape(-1)
+    ids64 = torch.where(ids64 < 0, ids64 + w.shape[0], ids64)  # negative ids count from the end, as indexing does
+    ids32 = ids64.to(torch.int32)  # uint32 bit pattern
+    with torch.cuda.device(dev):
+        out = torch.empty(tuple(ids.shape) + (K,), dtype=scales.dtype, device=dev)
+        rc = _lib.load().b200q_dequantize_rows(_ptr(w), _ptr(scales), _ptr(biases), _ptr(ids32), ids32.numel(),
+                                               _DT[scales.dtype], w.shape[0], K, group_size, bits, _ptr(out),
+                                               _stream(w))
+    _lib.check(rc)
+    return out
+
+
 # ------------------------------------------------------------------- quantized_matmul
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
                      biases: Optional[torch.Tensor] = None, transpose: bool = True,

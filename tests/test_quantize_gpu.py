@@ -123,3 +123,37 @@ def test_quantize_rounding_ties_and_extremes(dtype, g, bits):
         q, s, b = mb.quantize(to_torch(wd, dtype), g, bits)
         assert np.array_equal(from_torch(q).view(np.uint32), rq.view(np.uint32)), (ci, "wq")
         assert np.array_equal(from_torch(s), rs) and np.array_equal(from_torch(b), rb), (ci, "scales/biases")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("g,bits", [(32, 3), (64, 4), (128, 6), (64, 8), (32, 2), (128, 5)])
+def test_quantized_embedding_bit_exact_vs_oracle(dtype, g, bits):
+    """QuantizedEmbedding look-up (python/mlx/nn/layers/quantized.py:149-158) = the oracle's
+    dequantize of the indexed rows; negative ids count from the end, out-of-range ids give zeros."""
+    rng = np.random.default_rng(2500 + g + bits)
+    rows, K = 211, 768
+    w = O.to_dtype(edge_matrix(rng, rows, K, g), dtype)
+    wq, s, b = O.quantize(w, g, bits, dtype)
+    ids = rng.integers(0, rows, size=(5, 37))
+    ids[0, 0], ids[1, 1], ids[2, 2] = -1, -rows, rows - 1
+    pos = np.where(ids < 0, ids + rows, ids).reshape(-1)
+    ref = O.dequantize(wq[pos], s[pos], b[pos], g, bits, dtype).reshape(5, 37, K)
+    got = mb.quantized_embedding(torch.from_numpy(ids).cuda(), u32_to_torch(wq), to_torch(s, dtype),
+                                 to_torch(b, dtype), g, bits)
+    assert got.shape == (5, 37, K) and same(ref, from_torch(got))
+    bad = mb.quantized_embedding(torch.tensor([rows, 3, 2 ** 31 - 1], device="cuda"), u32_to_torch(wq),
+                                 to_torch(s, dtype), to_torch(b, dtype), g, bits)
+    assert not bad[0].any() and not bad[2].any()
+    assert same(from_torch(bad[1]), O.dequantize(wq[3:4], s[3:4], b[3:4], g, bits, dtype)[0])
+    empty = mb.quantized_embedding(torch.zeros(0, dtype=torch.int64, device="cuda"), u32_to_torch(wq),
+                                   to_torch(s, dtype), to_torch(b, dtype), g, bits)
+    assert empty.shape == (0, K)
+
+
+def test_quantized_embedding_rejects():
+    wq = torch.zeros(4, 32, dtype=torch.int32, device="cuda").view(torch.uint32)
+    s = torch.zeros(4, 4, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="integral"):
+        mb.quantized_embedding(torch.zeros(2, device="cuda"), wq, s, s, 64, 4)
+    with pytest.raises(ValueError, match="does not match"):
+        mb.quantized_embedding(torch.zeros(2, dtype=torch.int64, device="cuda"), wq, s[:, :2], s[:, :2], 64, 4)
