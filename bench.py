@@ -356,7 +356,11 @@ def main():
            "d2h_bytes_per_step": M_DEC * n_loc * 2, "ms_per_step": e2e_s * 1e3,
            "note": "b200q_qmm_host: pinned x -> device, kernel, y -> pinned host, synchronised every step; "
                    "weights stay resident in HBM"}
-    ok_check = bool(torch.allclose(y_host.float(), y.float().cpu(), rtol=0, atol=0))
+    # y holds the last kernel-only step on the same weights; partial sums combine in arrival order, so the
+    # two runs may differ in the last bfloat16 bit: compare within the matmul tolerance and report the gap
+    y_d, y_h = y.float().cpu(), y_host.float()
+    e2e_gap = float((y_h - y_d).abs().max())
+    ok_check = bool(torch.allclose(y_h, y_d, rtol=1e-2, atol=1e-2 * float(y_d.pow(2).mean().sqrt())))
 
     # ---- prefill configuration on the tensor-core path (rank-local shard)
     prefill = None
@@ -411,7 +415,7 @@ def main():
                        "timing": "CUDA events on the launching stream" + (", steps replayed from one CUDA graph" if (world == 1 or fused) else ""),
                        "parallelism": f"n-shard x{world}"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "prefill": prefill,
-            "cpu_baseline": cpu_baseline, "device_status": list(status), "e2e_matches_device": ok_check,
+            "cpu_baseline": cpu_baseline, "device_status": list(status), "e2e_matches_device": ok_check, "e2e_max_abs_gap": e2e_gap,
         }
         print(json.dumps(line))
     if world > 1:

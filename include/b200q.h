@@ -194,6 +194,25 @@ int b200q_gather_qmm_chain(const void* x, const uint32_t* wq1, const void* scale
                            int group_size, int bits, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * Gated expert MLP of a mixture-of-experts block over one set of index pairs, one sort:
+ *   g[i] = x[lhs_idx[i]] * dequant(w_gate[rhs_idx[i]])^T,  u[i] = x[lhs_idx[i]] * dequant(w_up[rhs_idx[i]])^T
+ *   h[i] = bfloat16( silu(g[i]) * u[i] )        silu(t) = t / (1 + exp(-t)), fp32 on the bfloat16 g and u
+ *   y[i] = h[i] * dequant(w_down[rhs_idx[i]])^T
+ * i.e. three gather_qmm (mlx/ops.cpp:5553-5629) and the activation between them, which the
+ * reference runs as separate operators with a sort and a scatter around each.
+ * w_gate, w_up [E, H, K1*bits/32]; w_down [E, N2, H*bits/32]; bfloat16, transpose form, K1 and H
+ * multiples of 128 (B200Q_ERR_UNSUPPORTED otherwise).  Index checks and status word as
+ * b200q_gather_qmm.
+ */
+size_t b200q_gather_qmm_swiglu_workspace_bytes(int64_t n_idx, int64_t E, int64_t M, int64_t H, int64_t K1);
+int b200q_gather_qmm_swiglu(const void* x, const uint32_t* wq_gate, const void* scales_gate, const void* biases_gate,
+                            const uint32_t* wq_up, const void* scales_up, const void* biases_up,
+                            const uint32_t* wq_down, const void* scales_down, const void* biases_down,
+                            const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* y, int dtype,
+                            int64_t x_batch, int64_t E, int64_t M, int64_t H, int64_t K1, int64_t N2,
+                            int group_size, int bits, void* ws, size_t ws_bytes, void* stream);
+
+/*
  * N-sharded linear with the all_gather fused into the matmul epilogue.  Replaces the pair
  * QuantizedAllToShardedLinear.__call__ + all_gather of the reference
  * (python/mlx/nn/layers/distributed.py:357-455, mlx/distributed/ops.cpp:62-84,

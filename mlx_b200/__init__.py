@@ -4,7 +4,8 @@ Drop-in for the reference's ``quantize`` / ``dequantize`` / ``quantized_matmul``
 ``gather_qmm`` operators; see ``mlx_b200.ops`` for the operator front-end and
 ``include/b200q.h`` for the C ABI of the CUDA library underneath.
 """
-__all__ = ["quantize", "dequantize", "quantized_matmul", "gather_qmm", "gather_qmm_chain", "quantized_embedding",
+__all__ = ["quantize", "dequantize", "quantized_matmul", "gather_qmm", "gather_qmm_chain", "gather_qmm_swiglu",
+           "quantized_embedding",
            "qmm_kernel_name"]
 
 

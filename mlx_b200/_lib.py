@@ -35,6 +35,8 @@ SIGNATURES = {
     "b200q_gather_qmm_chain_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "b200q_gather_qmm_chain": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i64, _i64, _i64, _i64, _i64,
                                     _i64, _i, _i, _vp, _sz, _vp]),
+    "b200q_gather_qmm_swiglu_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200q_gather_qmm_swiglu": (_i, [_vp] * 12 + [_i64, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_workspace_init": (_i, [_vp, _sz, _vp]),
     "b200q_read_status": (_i, [_vp, _sz, _vp, ctypes.POINTER(ctypes.c_uint32)]),
     "b200q_qmm_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i, _i, _i, _vp, _sz, _vp]),

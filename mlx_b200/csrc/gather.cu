@@ -318,3 +318,93 @@ extern "C" int b200q_gather_qmm_chain(const void* x, const uint32_t* wq1, const 
   g.x_sorted = h; g.wq = wq2; g.scales = scales2; g.biases = biases2; g.y = y; g.dst_row = dst; g.N = N2; g.K = N1;
   return qmm_tc_grouped(g, st);
 }
+
+// ---------------------------------------------------------------- gated expert MLP: down(silu(gate(x)) * up(x)), one sort
+namespace b200q {
+namespace {
+
+// g[i] = silu(g[i]) * u[i] on bf16 pairs, fp32 arithmetic, one rounding.
+__global__ void __launch_bounds__(256) swiglu_kernel(uint4* __restrict__ g, const uint4* __restrict__ u, int64_t n_vec) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  uint4 a = g[i];
+  const uint4 b = __ldg(u + i);
+  uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
+  const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float g0 = __uint_as_float(aw[k] << 16), g1 = __uint_as_float(aw[k] & 0xffff0000u);
+    const float u0 = __uint_as_float(bw[k] << 16), u1 = __uint_as_float(bw[k] & 0xffff0000u);
+    const float r0 = __fdividef(g0, 1.f + __expf(-g0)) * u0;
+    const float r1 = __fdividef(g1, 1.f + __expf(-g1)) * u1;
+    const __nv_bfloat162 r = __floats2bfloat162_rn(r0, r1);
+    aw[k] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  g[i] = a;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" size_t b200q_gather_qmm_swiglu_workspace_bytes(int64_t n_idx, int64_t E, int64_t M, int64_t H, int64_t K1) {
+  if (n_idx < 1 || E < 1 || M < 1 || H < 1 || K1 < 1) return 256;
+  const FastLayout L = fast_layout(n_idx, E, M, K1);
+  return L.total + 2 * align256((size_t)L.n_rows * H * 2);
+}
+
+extern "C" int b200q_gather_qmm_swiglu(const void* x, const uint32_t* wq_gate, const void* scales_gate, const void* biases_gate,
+                                       const uint32_t* wq_up, const void* scales_up, const void* biases_up,
+                                       const uint32_t* wq_down, const void* scales_down, const void* biases_down,
+                                       const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* y, int dtype,
+                                       int64_t x_batch, int64_t E, int64_t M, int64_t H, int64_t K1, int64_t N2,
+                                       int group_size, int bits, void* ws, size_t ws_bytes, void* stream) {
+  if (!valid_group(group_size) || !valid_bits(bits))
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_swiglu] group size must be 32, 64 or 128 and bits 2, 3, 4, 5, 6 or 8");
+  if (n_idx < 0 || x_batch < 0 || E < 1 || M < 0 || H < 0 || K1 < 0 || N2 < 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_swiglu] negative dimension.");
+  if (K1 % group_size != 0 || (K1 * bits) % 32 != 0 || H % group_size != 0 || (H * bits) % 32 != 0)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_swiglu] The shapes of the weight and scales are incompatible based on bits and group_size");
+  if (n_idx == 0 || M == 0 || N2 == 0) return B200Q_OK;
+  if (!x || !wq_gate || !scales_gate || !biases_gate || !wq_up || !scales_up || !biases_up || !wq_down || !scales_down ||
+      !biases_down || !lhs_idx || !rhs_idx || !y)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_swiglu] null pointer");
+  const bool aligned = !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wq_gate) | reinterpret_cast<uintptr_t>(wq_up) |
+                          reinterpret_cast<uintptr_t>(wq_down) | reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(y)) & 15);
+  if (!aligned || !fast_supported(dtype, n_idx, x_batch, E, M, H, K1, group_size, bits, 1) ||
+      !fast_supported(dtype, n_idx, n_idx, E, M, N2, H, group_size, bits, 1))
+    return fail(B200Q_ERR_UNSUPPORTED, "[gather_qmm_swiglu] only bfloat16 with K and the hidden width multiples of 128");
+  const size_t need = b200q_gather_qmm_swiglu_workspace_bytes(n_idx, E, M, H, K1);
+  if (!ws || ws_bytes < need)
+    return fail(B200Q_ERR_WORKSPACE, "[gather_qmm_swiglu] workspace of %zu bytes required, %zu given", need, ws_bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* status = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes);
+  const FastLayout L = fast_layout(n_idx, E, M, K1);
+  char* base = static_cast<char*>(ws);
+  Header* hdr = reinterpret_cast<Header*>(base + L.hdr);
+  int* sorted = reinterpret_cast<int*>(base + L.sorted);
+  int* dst = reinterpret_cast<int*>(base + L.dst);
+  MTileRec* mt = reinterpret_cast<MTileRec*>(base + L.mtiles);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + L.xs);
+  const size_t h_bytes = align256((size_t)L.n_rows * H * 2);
+  __nv_bfloat16* hg = reinterpret_cast<__nv_bfloat16*>(base + L.total - 256);
+  __nv_bfloat16* hu = reinterpret_cast<__nv_bfloat16*>(base + L.total - 256 + h_bytes);
+  gather_sort_kernel<<<1, 1024, 0, st>>>(lhs_idx, rhs_idx, (int)n_idx, (uint32_t)x_batch, (uint32_t)E, 0u, (uint32_t)E, (int)M,
+                                         L.nt, hdr, sorted, mt, y, (size_t)M * N2 * 2, status);
+  B200Q_LAUNCH_OK("gather_sort_kernel");
+  gather_rows_kernel<<<(unsigned)L.n_rows, 256, 0, st>>>((const __nv_bfloat16*)x, lhs_idx, hdr, sorted, (int)M, (int)K1, xs, dst);
+  B200Q_LAUNCH_OK("gather_rows_kernel");
+  GroupedArgs g{};
+  g.mtiles = mt; g.n_mtiles = &hdr->n_mtiles;
+  g.n_rows = L.n_rows; g.max_mtiles = L.max_mtiles; g.E = E;
+  g.group = group_size; g.bits = bits; g.nt = L.nt; g.status = status;
+  g.x_sorted = xs; g.dst_row = nullptr; g.N = H; g.K = K1;
+  g.wq = wq_gate; g.scales = scales_gate; g.biases = biases_gate; g.y = hg;
+  if (int rc = qmm_tc_grouped(g, st)) return rc;
+  g.wq = wq_up; g.scales = scales_up; g.biases = biases_up; g.y = hu;
+  if (int rc = qmm_tc_grouped(g, st)) return rc;
+  const int64_t n_vec = (int64_t)L.n_rows * H / 8;   // H is a multiple of 128
+  swiglu_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, st>>>(reinterpret_cast<uint4*>(hg), reinterpret_cast<const uint4*>(hu), n_vec);
+  B200Q_LAUNCH_OK("swiglu_kernel");
+  g.x_sorted = hg; g.wq = wq_down; g.scales = scales_down; g.biases = biases_down; g.y = y; g.dst_row = dst; g.N = N2; g.K = H;
+  return qmm_tc_grouped(g, st);
+}

@@ -403,3 +403,45 @@ def gather_qmm_chain(x: torch.Tensor, w1: torch.Tensor, scales1: torch.Tensor, b
                                         N1, K1, N2, group_size, bits, _ptr(ws), ws.numel(), _stream(x))
     _lib.check(rc)
     return y
+
+
+def gather_qmm_swiglu(x: torch.Tensor, gate, up, down, rhs_indices: torch.Tensor,
+                      lhs_indices: Optional[torch.Tensor] = None, group_size: Optional[int] = None,
+                      bits: Optional[int] = None) -> torch.Tensor:
+    """Gated expert MLP: gather_qmm(silu(gather_qmm(x, *gate)) * gather_qmm(x, *up), *down) over the same
+    index pairs with one sort (three mlx/ops.cpp:5553-5629 calls and the activation in the reference).
+    gate, up, down: (w, scales, biases) triples; gate/up [E, H, K1*bits/32], down [E, N2, H*bits/32];
+    x [B, M, K1] bf16; out: idx_shape + [M, N2]."""
+    group_size, bits = _mode_params("affine", group_size, bits, "gather_qmm_swiglu")
+    for t in (gate, up, down):
+        _validate_quantized_input("gather_qmm_swiglu", t[0], t[1], group_size, bits, t[2])
+    if x.dtype != torch.bfloat16 or x.ndim < 2:
+        raise ValueError("[gather_qmm_swiglu] x must be bfloat16 with at least two dimensions")
+    M, K1 = x.shape[-2], x.shape[-1]
+    H, N2 = gate[0].shape[-2], down[0].shape[-2]
+    if (gate[0].shape != up[0].shape or gate[0].shape[-1] * 32 // bits != K1 or down[0].shape[-1] * 32 // bits != H
+            or gate[0].shape[:-2] != down[0].shape[:-2]):
+        raise ValueError("[gather_qmm_swiglu] gate and up must map K1 -> H and down H -> N2 for the same experts")
+    dev = _require_cuda("gather_qmm_swiglu", x, *gate, *up, *down)
+    x_batch = x.numel() // max(M * K1, 1)
+    E = gate[0].numel() // max(gate[0].shape[-1] * H, 1)
+    rhs = rhs_indices.to(device=dev, dtype=torch.int64)
+    lhs = (torch.arange(x_batch, device=dev).reshape(tuple(x.shape[:-2])) if lhs_indices is None
+           else lhs_indices.to(device=dev, dtype=torch.int64))
+    lhs, rhs = torch.broadcast_tensors(lhs, rhs)
+    idx_shape = tuple(lhs.shape)
+    lhs32, rhs32 = lhs.contiguous().reshape(-1).to(torch.int32), rhs.contiguous().reshape(-1).to(torch.int32)
+    n_idx = lhs32.numel()
+    x = x.contiguous()
+    trip = lambda t: (t[0].contiguous(), t[1].to(torch.bfloat16).contiguous(), t[2].to(torch.bfloat16).contiguous())
+    gate, up, down = trip(gate), trip(up), trip(down)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        y = torch.empty(idx_shape + (M, N2), dtype=torch.bfloat16, device=dev)
+        need = lib.b200q_gather_qmm_swiglu_workspace_bytes(n_idx, E, M, H, K1)
+        ws = _workspaces.get(dev, need, "gather")
+        rc = lib.b200q_gather_qmm_swiglu(_ptr(x), *[_ptr(t) for t in gate], *[_ptr(t) for t in up], *[_ptr(t) for t in down],
+                                         _ptr(lhs32), _ptr(rhs32), n_idx, _ptr(y), _lib.BF16, x_batch, E, M, H, K1, N2,
+                                         group_size, bits, _ptr(ws), ws.numel(), _stream(x))
+    _lib.check(rc)
+    return y

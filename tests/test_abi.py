@@ -102,3 +102,27 @@ def test_gather_sharded_rejects_on_host():
     assert call(2, 2, 0, 4) == _lib.ERR_INVALID_ARGUMENT        # self outside the buffer list
     assert call(2, 0, 6, 4) == _lib.ERR_INVALID_ARGUMENT        # experts [6, 10) of 8
     assert call(2, 0, 0, 4, K=96) == _lib.ERR_INVALID_ARGUMENT  # K not a multiple of the group
+
+
+def test_embedding_and_gated_mlp_reject_on_host():
+    lib = _lib.load()
+    d = ctypes.c_void_p(4096)
+    rows_call = lambda **kw: lib.b200q_dequantize_rows(
+        d, d, d, d, kw.get("n", 4), kw.get("dtype", _lib.BF16), 16, kw.get("K", 256), kw.get("group", 64),
+        kw.get("bits", 4), d, None)
+    assert rows_call(group=48) == _lib.ERR_INVALID_ARGUMENT
+    assert rows_call(bits=7) == _lib.ERR_INVALID_ARGUMENT
+    assert rows_call(K=100) == _lib.ERR_INVALID_ARGUMENT
+    assert rows_call(dtype=9) == _lib.ERR_INVALID_ARGUMENT
+    assert rows_call(n=-1) == _lib.ERR_INVALID_ARGUMENT
+    assert rows_call(n=0) == 0                                   # nothing to look up
+    glu = lambda **kw: lib.b200q_gather_qmm_swiglu(
+        d, d, d, d, d, d, d, d, d, d, d, d, kw.get("n", 8), d, kw.get("dtype", _lib.BF16), 8, 4, 1, kw.get("H", 256),
+        kw.get("K1", 256), 128, kw.get("group", 64), kw.get("bits", 4), d, kw.get("ws", 1 << 24), None)
+    assert glu(group=16) == _lib.ERR_INVALID_ARGUMENT
+    assert glu(H=96) == _lib.ERR_INVALID_ARGUMENT               # hidden width not a multiple of the group
+    assert glu(n=0) == 0
+    assert glu(dtype=_lib.F32) == _lib.ERR_UNSUPPORTED          # bfloat16 only
+    assert glu(ws=256) == _lib.ERR_WORKSPACE
+    assert lib.b200q_gather_qmm_swiglu_workspace_bytes(8, 4, 1, 256, 256) > lib.b200q_gather_qmm_workspace_bytes(
+        _lib.BF16, 8, 8, 4, 1, 256, 256, 64, 4, 1)

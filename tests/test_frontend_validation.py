@@ -81,3 +81,23 @@ def test_no_cpu_fallback():
         mb.quantized_matmul(x, w, s, b)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         mb.quantize(torch.zeros(4, 256))
+
+
+def test_quantized_embedding_and_swiglu_errors():
+    w, s = u32(8, 32), torch.zeros(8, 4, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="integral"):
+        mb.quantized_embedding(torch.zeros(3), w, s, s, 64, 4)
+    with pytest.raises(ValueError, match="does not match"):
+        mb.quantized_embedding(torch.zeros(3, dtype=torch.int64), w, s[:, :2], s[:, :2], 64, 4)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        mb.quantized_embedding(torch.zeros(3, dtype=torch.int64), w, s, s, 64, 4)
+    x = torch.zeros(4, 1, 256, dtype=torch.bfloat16)
+    gate = (u32(2, 128, 32), torch.zeros(2, 128, 4, dtype=torch.bfloat16), torch.zeros(2, 128, 4, dtype=torch.bfloat16))
+    down = (u32(2, 256, 16), torch.zeros(2, 256, 2, dtype=torch.bfloat16), torch.zeros(2, 256, 2, dtype=torch.bfloat16))
+    idx = torch.zeros(4, dtype=torch.int64)
+    with pytest.raises(ValueError, match="bfloat16"):
+        mb.gather_qmm_swiglu(x.float(), gate, gate, down, rhs_indices=idx)
+    with pytest.raises(ValueError, match="same experts"):
+        mb.gather_qmm_swiglu(x, gate, down, down, rhs_indices=idx)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        mb.gather_qmm_swiglu(x, gate, gate, down, rhs_indices=idx)

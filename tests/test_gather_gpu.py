@@ -198,3 +198,33 @@ def test_gather_chain_vs_two_calls_and_oracle(E, tokens, topk, K1, N1, N2):
                        np.arange(tokens * topk, dtype=np.uint32), rhs.reshape(-1).astype(np.uint32), True, g, 4, "f32")
     ok, rel = qmm_close(O.to_f32(from_torch(y.contiguous()), dtype).reshape(ref.shape), ref)
     assert ok, rel
+
+
+@pytest.mark.parametrize("E,tokens,topk,K1,H,N2", [(4, 48, 2, 256, 384, 256), (8, 160, 2, 512, 1024, 512)])
+def test_gather_swiglu_vs_three_calls_and_oracle(E, tokens, topk, K1, H, N2):
+    """Gated expert MLP with one sort: the same as three gather_qmm calls with the activation
+    between them (fp32 silu(g)*u of the bfloat16 products, one rounding), and its last product
+    close to the oracle's on the same activations."""
+    g, dtype = 64, "bf16"
+    trip = lambda seed, shape: O.quantize(make_w(seed, shape, dtype), g, 4, dtype)
+    gate, up, down = trip(60, (E, H, K1)), trip(61, (E, H, K1)), trip(62, (E, N2, H))
+    x = make_x(63, (tokens, 1, K1), dtype)
+    rng = np.random.default_rng(10)
+    rhs = rng.integers(0, E, size=(tokens, topk)).astype(np.int64)
+    t = lambda a: to_torch(a, dtype)
+    dev = lambda q: (u32_to_torch(q[0]), t(q[1]), t(q[2]))
+    lhs = torch.arange(tokens).reshape(tokens, 1).expand(tokens, topk)
+    rhs_t = torch.from_numpy(rhs)
+    y = mb.gather_qmm_swiglu(t(x), dev(gate), dev(up), dev(down), rhs_indices=rhs_t, lhs_indices=lhs)
+    assert tuple(y.shape) == (tokens, topk, 1, N2)
+    hg = mb.gather_qmm(t(x), *dev(gate), lhs_indices=lhs, rhs_indices=rhs_t).float()
+    hu = mb.gather_qmm(t(x), *dev(up), lhs_indices=lhs, rhs_indices=rhs_t).float()
+    h = (hg / (1.0 + torch.exp(-hg)) * hu).to(torch.bfloat16).reshape(tokens * topk, 1, H)
+    y3 = mb.gather_qmm(h, *dev(down), rhs_indices=rhs_t.reshape(-1))
+    # the device's fast exp/divide may move an activation by one bfloat16 step: compare within tolerance
+    ok, rel = qmm_close(y.float().cpu().numpy().reshape(-1, N2), y3.float().cpu().numpy().reshape(-1, N2))
+    assert ok, rel
+    ref = O.gather_qmm(O.to_f32(from_torch(h.contiguous()), dtype), down[0], O.to_f32(down[1], dtype), O.to_f32(down[2], dtype),
+                       np.arange(tokens * topk, dtype=np.uint32), rhs.reshape(-1).astype(np.uint32), True, g, 4, "f32")
+    ok, rel = qmm_close(O.to_f32(from_torch(y.contiguous()), dtype).reshape(ref.shape), ref)
+    assert ok, rel
