@@ -149,6 +149,18 @@ inline void dequantize(const ArrayView& wq, const ArrayView& scales, const Array
                                  group_size, bits, out.data, stream));
 }
 
+// out[i, :] = dequantize(row ids[i]) : QuantizedEmbedding.__call__ (python/mlx/nn/layers/quantized.py:149-158)
+inline void quantized_embedding(const ArrayView& ids, const ArrayView& wq, const ArrayView& scales, const ArrayView& biases,
+                                ArrayView& out, int group_size = 64, int bits = 4, void* stream = nullptr) {
+  detail::validate_quantized_input("quantized_embedding", wq, scales, biases, group_size, bits);
+  if (ids.dtype != Dtype::uint32) throw std::invalid_argument("[quantized_embedding] ids must be uint32.");
+  if (wq.ndim() != 2) throw std::invalid_argument("[quantized_embedding] the table must be a 2-D packed matrix");
+  const int64_t K = wq.dim(-1) * 32 / bits;
+  detail::check(b200q_dequantize_rows(static_cast<const uint32_t*>(wq.data), scales.data, biases.data,
+                                      static_cast<const uint32_t*>(ids.data), ids.size(), (int)scales.dtype, wq.dim(0), K,
+                                      group_size, bits, out.data, stream));
+}
+
 // x [.., M, K] against one matrix w (2-D) or a stack of matrices with x's batch shape  (mlx/ops.cpp:4784-4834)
 inline void quantized_matmul(const ArrayView& x, const ArrayView& w, const ArrayView& scales, const ArrayView& biases, ArrayView& out,
                              const Workspace& ws, bool transpose = true, int group_size = 64, int bits = 4,

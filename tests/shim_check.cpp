@@ -73,6 +73,17 @@ int main() {
     auto w1 = view(Dtype::float32, {64});
     quantize(w1, w, s, b);
   });
+  bad += expect_invalid("embedding ids dtype", "ids must be uint32", [&] {
+    auto ids = view(Dtype::float32, {5});
+    auto eo = view(Dtype::bfloat16, {5, 512});
+    quantized_embedding(ids, w, s, b, eo);
+  });
+  bad += expect_invalid("embedding table shapes", "Scales and biases should have the same shape", [&] {
+    auto ids = view(Dtype::uint32, {5});
+    auto b2 = view(Dtype::bfloat16, {256, 4});
+    auto eo = view(Dtype::bfloat16, {5, 512});
+    quantized_embedding(ids, w, s, b2, eo);
+  });
   bad += expect_invalid("gather index dtype", "Indices must be integral", [&] {
     auto xe = view(Dtype::bfloat16, {4, 1, 512});
     auto we = view(Dtype::uint32, {2, 256, 64});
