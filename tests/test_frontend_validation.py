@@ -101,3 +101,13 @@ def test_quantized_embedding_and_swiglu_errors():
         mb.gather_qmm_swiglu(x, gate, down, down, rhs_indices=idx)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         mb.gather_qmm_swiglu(x, gate, gate, down, rhs_indices=idx)
+
+
+def test_grad_wrapper_has_no_cpu_fallback():
+    from mlx_b200 import grad
+    x = torch.zeros(2, 256, requires_grad=True)
+    w, s, b = u32(8, 32), torch.zeros(8, 4), torch.zeros(8, 4)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        grad.quantized_matmul(x, w, s, b)
+    with pytest.raises(ValueError):
+        grad.quantized_matmul(x, w, s, b, group_size=48)
