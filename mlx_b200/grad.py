@@ -58,3 +58,51 @@ def jvp(x_tangent: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: 
         transpose: bool = True, group_size: Optional[int] = None, bits: Optional[int] = None) -> torch.Tensor:
     """QuantizedMatmul::jvp (mlx/primitives.cpp:3600-3619): the same product applied to the tangent of x."""
     return ops.quantized_matmul(x_tangent, w, scales, biases, transpose, group_size, bits)
+
+
+class _GatherQmmFn(torch.autograd.Function):
+    """GatherQMM::vjp wrt x (mlx/primitives.cpp:3718-3772): the cotangent goes through gather_qmm with
+    the transposition flipped and the same rhs_indices, then its rows are added into x at lhs_indices."""
+
+    @staticmethod
+    def forward(ctx, x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits):
+        ctx.save_for_backward(w, scales, biases, lhs_indices, rhs_indices)
+        ctx.cfg = (bool(transpose), group_size, bits, tuple(x.shape), x.dtype)
+        return ops.gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits)
+
+    @staticmethod
+    def backward(ctx, cotangent):
+        w, scales, biases, lhs_indices, rhs_indices = ctx.saved_tensors
+        transpose, group_size, bits, x_shape, x_dtype = ctx.cfg
+        if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+            raise NotImplementedError("[gather_qmm] gradients wrt scales and biases are not provided")
+        if not ctx.needs_input_grad[0]:
+            return (None,) * 9
+        idx_shape = tuple(cotangent.shape[:-2])
+        M = cotangent.shape[-2]
+        rhs = torch.broadcast_to(rhs_indices, idx_shape).reshape(-1)
+        lhs = torch.broadcast_to(lhs_indices, idx_shape).reshape(-1).to(torch.int64)
+        g = ops.gather_qmm(cotangent.reshape((-1, M, cotangent.shape[-1])).contiguous(), w, scales, biases, None, rhs,
+                           not transpose, group_size, bits)          # [n_idx, M, K]
+        dx = torch.zeros((max(1, torch.Size(x_shape[:-2]).numel()),) + tuple(x_shape[-2:]), dtype=torch.float32,
+                         device=g.device)
+        dx.index_add_(0, lhs, g.float())
+        return (dx.to(x_dtype).reshape(x_shape),) + (None,) * 8
+
+
+def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+               lhs_indices: Optional[torch.Tensor] = None, rhs_indices: Optional[torch.Tensor] = None,
+               transpose: bool = True, group_size: Optional[int] = None, bits: Optional[int] = None,
+               mode: str = "affine") -> torch.Tensor:
+    """ops.gather_qmm with autograd support for x."""
+    group_size, bits = ops._mode_params(mode, group_size, bits, "gather_qmm")
+    if lhs_indices is None and rhs_indices is None:
+        return quantized_matmul(x, w, scales, biases, transpose, group_size, bits)
+    dev = x.device
+    if lhs_indices is None:
+        lhs_indices = torch.arange(max(1, torch.Size(x.shape[:-2]).numel()), device=dev).reshape(tuple(x.shape[:-2]))
+    if rhs_indices is None:
+        rhs_indices = torch.arange(max(1, torch.Size(w.shape[:-2]).numel()), device=dev).reshape(tuple(w.shape[:-2]))
+    lhs_indices, rhs_indices = torch.broadcast_tensors(lhs_indices.to(dev), rhs_indices.to(dev))
+    return _GatherQmmFn.apply(x, w, scales, biases, lhs_indices.contiguous(), rhs_indices.contiguous(), transpose,
+                              group_size, bits)

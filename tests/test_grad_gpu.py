@@ -60,3 +60,27 @@ def test_no_gradient_wrt_packed_weights():
     x = torch.randn(2, 256, device="cuda", requires_grad=True)
     y = grad.quantized_matmul(x, wq, s, b)
     assert y.requires_grad and not wq.requires_grad
+
+
+@pytest.mark.parametrize("transpose", [True, False])
+def test_gather_qmm_vjp_matches_dense_autograd(transpose):
+    """d x of gather_qmm (mlx/primitives.cpp:3718-3772; python/tests/test_quantized.py:755-842 checks
+    the same identity): rows of the flipped product added back at lhs_indices."""
+    torch.manual_seed(11)
+    E, B, M, N, K, g, bits = 4, 6, 2, 256, 128, 64, 4
+    w = torch.randn((E, N, K) if transpose else (E, K, N), device="cuda")
+    wq, s, b = mb.quantize(w, g, bits)
+    x = torch.randn(B, M, K, device="cuda", requires_grad=True)
+    lhs = torch.tensor([0, 0, 3, 5, 5, 5, 2], device="cuda")
+    rhs = torch.tensor([1, 3, 0, 2, 2, 1, 3], device="cuda")
+    y = grad.gather_qmm(x, wq, s, b, lhs, rhs, transpose, g, bits)
+    assert tuple(y.shape) == (7, M, N)
+    c = torch.randn_like(y)
+    (dx,) = torch.autograd.grad(y, (x,), c)
+    wd = mb.dequantize(wq, s, b, g, bits).double()
+    x64 = x.detach().double().requires_grad_(True)
+    y64 = torch.stack([x64[l] @ (wd[r].transpose(0, 1) if transpose else wd[r]) for l, r in zip(lhs.tolist(), rhs.tolist())])
+    (rx,) = torch.autograd.grad(y64, (x64,), c.double())
+    assert float((y.detach().double() - y64.detach()).abs().max()) <= 1e-3 * float(y64.detach().abs().max())
+    assert dx.shape == x.shape and float((dx.double() - rx).abs().max()) <= 1e-3 * float(rx.abs().max())
+    assert not dx[1].any() and not dx[4].any()       # rows no index pair reads get no gradient
