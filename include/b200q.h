@@ -300,11 +300,25 @@ int b200q_gguf_repack(const void* blocks, int gguf_type, int64_t n_blocks, uint3
 
 /*
  * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
- * launch for this problem ("qmv_mma", "qmv_stream", "qmv_bulk", "qmv_tc", "qmm_tcgen05",
+ * launch for this problem ("qmv_rows", "qmv_mma", "qmv_stream", "qmv_bulk", "qmv_tc", "qmm_tcgen05",
  * "qmm_generic").
  */
 const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
                                   int group_size, int bits, int transpose);
+
+/*
+ * Process-wide promise about the stream order around matmul calls: on != 0 says that the packed
+ * weights, scales and biases passed to b200q_qmm / b200q_qmm_sharded are never written by the
+ * operation that directly precedes the call on its stream (the normal case in inference: they
+ * are constants).  The decode kernel then requests them while the previous kernel of the stream
+ * is still finishing (programmatic dependent launch) instead of after it; x, y and the workspace
+ * are always touched only after the previous kernel has completed.  Default 0 (or the
+ * environment variable B200Q_WEIGHTS_CONSTANT=1).  With the promise broken (e.g. b200q_quantize
+ * directly followed by b200q_qmm on the same buffers) the matmul may read stale weights.
+ * The reference has no counterpart: its command encoder orders whole kernels
+ * (mlx/backend/cuda/device.cpp:243-359).
+ */
+void b200q_set_weights_constant(int on);
 
 /* Number of kernel launches issued by this library on the calling thread so far. */
 uint64_t b200q_launch_count(void);

@@ -54,6 +54,7 @@ SIGNATURES = {
     "b200q_gguf_repack": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp]),
     "b200q_qmm_kernel_name": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i, _i, _i]),
     "b200q_launch_count": (ctypes.c_uint64, []),
+    "b200q_set_weights_constant": (None, [_i]),
 }
 
 _lib = None

@@ -32,7 +32,7 @@ void count_launch(int n) { g_launches += (uint64_t)n; }
 
 namespace {
 
-enum class Path { QmvStream, QmvTc, QmvBulk, Qmv, Tc, Qvm, Generic };
+enum class Path { QmvRows, QmvStream, QmvTc, QmvBulk, Qmv, Tc, Qvm, Generic };
 
 int check_qmm_args(const char* tag, const QmmArgs& a) {
   if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
@@ -60,7 +60,7 @@ int qmv_override() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_QMV_IMPL");
-    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : (strcmp(e, "stream") == 0 ? 4 : 0))));
+    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : (strcmp(e, "stream") == 0 ? 4 : (strcmp(e, "rows") == 0 ? 5 : 0)))));
   }
   return v;
 }
@@ -79,6 +79,7 @@ Path choose(const QmmArgs& a) {
   if (force_tc() && qmm_tc_supported(a)) return Path::Tc;  // tuning aid: tensor-memory path for any M
   if (ov == 3 && qmv_tc_supported(a)) return Path::QmvTc;
   if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
+  if ((ov == 0 || ov == 5) && qmv_rows_supported(a)) return Path::QmvRows;
   if (qmv_stream_supported(a) && (ov == 4 || (ov == 0 && qmv_stream_profitable(a)))) return Path::QmvStream;
   if (qmv_mma_supported(a)) return Path::Qmv;
   if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
@@ -112,6 +113,7 @@ int run_qmm(const QmmArgs& a, cudaStream_t st) {
   if (!a.x || !a.wq || !a.scales || !a.biases || !a.y)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null pointer");
   switch (choose(a)) {
+    case Path::QmvRows: return qmv_rows(a, st);
     case Path::QmvStream: return qmv_stream(a, st);
     case Path::QmvTc: return qmv_tc(a, st);
     case Path::QmvBulk: return qmv_bulk(a, st);
@@ -130,6 +132,8 @@ using namespace b200q;
 extern "C" int b200q_version(void) { return B200Q_VERSION; }
 extern "C" const char* b200q_last_error(void) { return g_err; }
 extern "C" uint64_t b200q_launch_count(void) { return g_launches; }
+
+extern "C" void b200q_set_weights_constant(int on) { set_weights_constant(on); }
 
 extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,
                                             int group_size, int bits, int transpose) {
@@ -170,6 +174,7 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
                         group_size, bits, transpose, 0, nullptr, 0);
   if (check_qmm_args("quantized_matmul", a)) return "invalid";
   switch (choose(a)) {
+    case Path::QmvRows: return "qmv_rows";
     case Path::QmvStream: return "qmv_stream";
     case Path::QmvTc: return "qmv_tc";
     case Path::QmvBulk: return "qmv_bulk";
@@ -259,6 +264,7 @@ extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* 
   if (a.M == 0 || a.N == 0) return B200Q_OK;
   if (!x || !wq || !scales || !biases) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a.K > 0 && qmv_override() == 0 && qmv_rows_supported(a)) return qmv_rows(a, st);
   if (a.K > 0 && qmv_mma_supported(a)) return qmv_mma(a, st);
   if (a.K > 0 && qmm_tc_supported(a)) return qmm_tc(a, st);
   return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");

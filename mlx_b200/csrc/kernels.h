@@ -70,6 +70,13 @@ bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a);
 int qmv_mma(const QmmArgs& a, cudaStream_t st);
 
+// qmv_rows.cu : decode path, bits 2/4/8, every CTA owns whole weight rows (bulk-copy ring, no scratch)
+bool qmv_rows_supported(const QmmArgs& a);
+int qmv_rows(const QmmArgs& a, cudaStream_t st);
+// Promise that weights are not written by the stream operation preceding a matmul (see qmv_rows.cu).
+bool weights_constant();
+void set_weights_constant(int on);
+
 // qvm.cu : non-transposed decode (M <= 4, bits 2/4/8): y = x * dequant(W[K, N])
 bool qvm_supported(const QmmArgs& a);
 size_t qvm_workspace_bytes(const QmmArgs& a);

@@ -175,6 +175,7 @@ struct QmvParams {
   long long total_steps;
   int tilebuf_blocks;  // row blocks a CTA span can touch
   int group_shift;     // log2(group_size / 32)
+  int early;           // weights may be requested before the previous kernel of the stream has ended
 };
 
 template <int BITS, int MT, int RT>
@@ -247,14 +248,16 @@ qmv_mma_kernel(const QmvParams p) {
       set_rows();
     }
   };
+  // Programmatic dependent launch: when the caller has promised that weights are constants
+  // (b200q_set_weights_constant), the first weight loads run while the previous kernel of the
+  // stream (e.g. the previous decode step) is still finishing; otherwise they too wait for it,
+  // since that kernel may be the one that wrote them (a quantize, a cast, a repack).
+  // Everything that kernel may produce (x) or still use (y, the workspace) is touched only after
+  // the wait.  Without the launch attribute the instruction returns at once.
+  if (!p.early) asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
   for (int d = 0; d < kPipe; ++d)
     if (s0 + d < s1) issue(d);
-
-  // Programmatic dependent launch: the weight loads above read constants, so they may run while
-  // the previous kernel of the stream (e.g. the previous decode step) is still finishing.
-  // Everything that kernel may produce (x) or still use (y, the workspace) is touched only after
-  // this point.  Without the launch attribute the instruction returns at once.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- stage x in B-fragment order; zero the tile buffer -------------------------
   {
@@ -545,6 +548,7 @@ int qmv_mma(const QmmArgs& a, cudaStream_t st) {
     return fail(B200Q_ERR_WORKSPACE, "[quantized_matmul] workspace must be 16-byte aligned");
   pl.prm.counters = reinterpret_cast<uint32_t*>(a.ws);
   pl.prm.partial = reinterpret_cast<float*>(static_cast<char*>(a.ws) + counters_bytes(a.N));
+  pl.prm.early = weights_constant() ? 1 : 0;
   int rc = B200Q_ERR_UNSUPPORTED;
   B200Q_DISPATCH_BITS(a.bits, BITS, { rc = launch<BITS>(pl, st); });
   return rc;
@@ -613,8 +617,13 @@ extern "C" int b200q_qmm_decode_static(const void* x, const uint32_t* wq, const 
   a.x = x; a.wq = wq; a.scales = scales; a.biases = biases; a.y = y;
   a.dtype = dtype; a.batch = 1; a.M = M; a.N = N; a.K = K;
   a.group = group_size; a.bits = bits; a.transpose = true; a.w_batched = false;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15))
+    return fail(B200Q_ERR_UNSUPPORTED, "[decode_static] x and wq must be 16-byte aligned");
   if (!qmv_mma_supported(a))
-    return fail(B200Q_ERR_UNSUPPORTED, "[decode_static] x and wq must be 16-byte aligned and x must fit in shared memory");
+    return fail(B200Q_ERR_UNSUPPORTED,
+                "[decode_static] the activations do not fit in shared memory: M=%lld rows of K=%lld need %lld KB "
+                "of the 220 KB a thread block may use; use b200q_qmm with a caller workspace",
+                (long long)M, (long long)K, (long long)((M > 8 ? 2 : 1) * (K / 128) * 2048 / 1024));
   void* scratch = nullptr;
   if (int rc = static_scratch_ptr(&scratch)) return rc;  // first call on a device: set-up (not capturable)
   const size_t used = qmv_mma_workspace_bytes(a);  // <= kStaticScratchBytes by the N check above

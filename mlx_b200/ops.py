@@ -66,6 +66,57 @@ class _Workspaces:
 
 _workspaces = _Workspaces()
 
+_STATUS_TEXT = {
+    1: "gather index out of range (that output was zeroed)",
+    2: "bounded wait expired in the bulk-copy ring of a decode kernel",
+    3: "bounded wait expired in the tcgen05 prefill kernel",
+    4: "bounded wait expired in the tcgen05 decode kernel",
+    5: "bounded wait expired in the TMA ring of the stream decode kernel",
+    6: "bounded wait for a peer GPU's completion flag expired: the gathered output is incomplete",
+    7: "bounded wait expired in the row-owning decode kernel",
+}
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel of this library gave up on a bounded wait (or met a bad gather index) and said so
+    in the status word of its workspace: the outputs of that call are not valid."""
+
+    def __init__(self, code: int, words, where: str):
+        self.code, self.words = int(code), tuple(int(w) for w in words)
+        super().__init__(f"b200q device status {self.code} ({_STATUS_TEXT.get(self.code, 'unknown')}) in the "
+                         f"{where} workspace; status words {self.words}")
+
+
+def read_workspace_status(ws: torch.Tensor, stream_ptr: int, where: str = "caller") -> None:
+    """Synchronises the stream, reads and clears the status word at the end of `ws`, and raises
+    DeviceStatusError if it is non-zero, after zeroing the whole workspace again (an aborted
+    kernel leaves counters and partial sums behind that would corrupt every later call)."""
+    lib = _lib.load()
+    st = (ctypes.c_uint32 * 4)()
+    sp = ctypes.c_void_p(stream_ptr)
+    with torch.cuda.device(ws.device):
+        _lib.check(lib.b200q_read_status(ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp, st))
+        if st[0] != 0:
+            _lib.check(lib.b200q_workspace_init(ctypes.c_void_p(ws.data_ptr()), ws.numel(), sp))
+            raise DeviceStatusError(st[0], list(st), where)
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Checked mode on request: synchronises every stream this module has launched on (for
+    `device`, or all devices) and raises DeviceStatusError if any kernel reported a failure since
+    the last check.  The operators themselves never synchronise; call this where the results are
+    about to be consumed on the host, or set B200Q_CHECK_STATUS=1 to have every operator call do
+    it before it returns (debugging: it serialises host and device)."""
+    for (dev_index, stream_ptr, op), ws in list(_workspaces._bufs.items()):
+        if device is not None and torch.device(device).index not in (None, dev_index):
+            continue
+        read_workspace_status(ws, stream_ptr, op)
+
+
+def _checked() -> bool:
+    import os
+    return os.environ.get("B200Q_CHECK_STATUS", "0") == "1"
+
 
 def _mode_params(mode: str, group_size, bits, tag: str) -> Tuple[int, int]:
     if mode not in _MODES:
@@ -298,6 +349,8 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
         rc = lib.b200q_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(y), _DT[dtype], batch, M, N, K,
                            group_size, bits, int(transpose), w_stride, _ptr(ws), ws.numel(), _stream(x))
     _lib.check(rc)
+    if _checked():
+        read_workspace_status(ws, torch.cuda.current_stream(dev).cuda_stream, "qmm")
     return y.squeeze(-2) if vector else y
 
 
@@ -354,6 +407,8 @@ def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: O
                                   _ptr(y), _DT[out_type], x_batch, E, M, N, K, group_size, bits, int(transpose),
                                   flags, _ptr(ws), ws.numel(), _stream(x))
     _lib.check(rc)
+    if _checked():
+        read_workspace_status(ws, torch.cuda.current_stream(dev).cuda_stream, "gather")
     return y
 
 

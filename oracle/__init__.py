@@ -32,16 +32,30 @@ _NP = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
 _lib = None
 
 
+def reference_root() -> str | None:
+    """Checkout of the reference project: $REF_ROOT, else a directory named `reference` next to
+    this repository.  None when neither holds the CPU translation unit."""
+    cands = [os.environ.get("REF_ROOT"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "mlx", "backend", "cpu", "quantized.cpp")):
+            return c
+    return None
+
+
 def build(with_reference: bool | None = None) -> None:
     """Compile the C restatement and, when the reference checkout is present, the
     reference-driven binary.  Building the checker is not using it."""
-    ref_root = os.environ.get("REF_ROOT", "/root/reference")
+    ref_root = reference_root()
     targets = ["qref"]
     if with_reference is None:
-        with_reference = os.path.isdir(os.path.join(ref_root, "mlx", "backend", "cpu"))
+        with_reference = ref_root is not None
+    cmd = ["make", "-s", "-C", _HERE]
     if with_reference:
+        if ref_root is None:
+            raise RuntimeError("the reference checkout was not found: set REF_ROOT")
         targets.append("ref")
-    subprocess.run(["make", "-s", "-C", _HERE, f"REF_ROOT={ref_root}"] + targets, check=True)
+        cmd.append(f"REF_ROOT={ref_root}")
+    subprocess.run(cmd + targets, check=True)
 
 
 def have_reference() -> bool:
@@ -237,6 +251,22 @@ def ref_gather_qmm(x, wq, scales, biases, lhs, rhs, transpose=True, group_size=6
 
 # ----------------------------------------------------------------------------- GGUF repack
 GGUF_BLOCK_BYTES = {2: 18, 3: 20, 8: 34}   # Q4_0, Q4_1, Q8_0
+REF_GGUF_BIN = os.path.join(_HERE, "_ref", "ref_gguf")
+
+
+def have_reference_gguf() -> bool:
+    return os.path.isfile(REF_GGUF_BIN) and os.access(REF_GGUF_BIN, os.X_OK)
+
+
+def ref_gguf_unpack(quants: np.ndarray) -> np.ndarray:
+    """The reference's own unpack_32_4 (mlx/io/gguf_quants.cpp:13-31) on uint8 [n, 16] quant
+    bytes of Q4 blocks -> uint8 [n, 16] in the affine layout's nibble order."""
+    quants = np.ascontiguousarray(quants, dtype=np.uint8).reshape(-1, 16)
+    with tempfile.TemporaryDirectory() as d:
+        fi, fo = os.path.join(d, "i.bin"), os.path.join(d, "o.bin")
+        quants.tofile(fi)
+        subprocess.run([REF_GGUF_BIN, "unpack", str(quants.shape[0]), fi, fo], check=True)
+        return np.fromfile(fo, dtype=np.uint8).reshape(-1, 16)
 
 
 def gguf_repack(blocks: np.ndarray, gguf_type: int):

@@ -4,12 +4,14 @@
  *   qref_gguf_repack   extract_q4_0_data / extract_q4_1_data / extract_q8_0_data and
  *                      unpack_32_4          mlx/io/gguf_quants.cpp:11-102
  *
- * Parity status: UNPINNED for this file.  The reference source includes the third-party
- * gguflib header, which its build fetches from the network and which is absent from the
- * checkout, so it cannot be compiled here, and the reference holds no stored vectors for it.
- * The functions below restate its three loops; tests/test_formats.py checks them against
- * hand-derived known-answer blocks and against the format definition
- * (value = d * (q - 8) for Q4_0, d * q + m for Q4_1, d * q for Q8_0).
+ * Parity status: the nibble order of the 4-bit blocks is PINNED to the reference's own
+ * unpack_32_4, compiled from the reference checkout with the third-party gguflib header replaced
+ * by declarations (oracle/ref_gguf_driver.cpp, oracle/stub/gguflib.h): golden vectors in
+ * tests/golden/gguf_unpack_golden.npz plus a live comparison where the binary exists.  The loops
+ * around it (scale / bias in float16, sign flip of Q8_0) take the reference's array objects, whose
+ * runtime cannot be linked here; they are restated and checked against the format definition
+ * (value = d * (q - 8) for Q4_0, d * q + m for Q4_1, d * q for Q8_0), which fixes them up to the
+ * float16 rounding of the bias (exact for Q4_0 and Q8_0: -8 d and -128 d are exact).
  *
  * Block layouts (32 weights per block):
  *   Q4_0  | f16 d | 16 bytes: byte j = weight j (low nibble), weight j + 16 (high nibble) |   18 B

@@ -1,5 +1,6 @@
-"""Generates tests/golden/affine_golden.npz by running the reference project's own CPU
-code (oracle/_ref/ref_oracle, compiled from the reference checkout by oracle/Makefile).
+"""Generates tests/golden/affine_golden.npz and tests/golden/gguf_unpack_golden.npz by running
+the reference project's own CPU code (oracle/_ref/ref_oracle and oracle/_ref/ref_gguf, compiled
+from the reference checkout by oracle/Makefile).
 
     python tests/golden/make_golden.py
 
@@ -17,6 +18,7 @@ sys.path.insert(0, ROOT)
 import oracle as O  # noqa: E402
 
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "affine_golden.npz")
+OUT_GGUF = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gguf_unpack_golden.npz")
 
 
 def special_rows(w, g):
@@ -65,6 +67,12 @@ def main():
         data[f"gather/{k}"] = v
     np.savez_compressed(OUT, **data)
     print(OUT, os.path.getsize(OUT), "bytes,", len(data), "arrays")
+    # GGUF: the reference's nibble re-ordering of Q4 blocks (oracle/_ref/ref_gguf)
+    assert O.have_reference_gguf(), "reference GGUF binary missing"
+    quants = np.random.default_rng(20240301).integers(0, 256, (64, 16), dtype=np.uint8)
+    quants[0] = np.arange(16) | (np.arange(16, 32) % 16) << 4     # weight j -> j % 16, readable by eye
+    np.savez_compressed(OUT_GGUF, quants=quants, unpacked=O.ref_gguf_unpack(quants))
+    print(OUT_GGUF, os.path.getsize(OUT_GGUF), "bytes")
 
 
 if __name__ == "__main__":

@@ -64,8 +64,8 @@ def test_qmm_rejects_on_host():
 def test_kernel_selection_names():
     lib = _lib.load()
     name = lambda M, N, K, dt=_lib.BF16, tr=1, bits=4, g=64: lib.b200q_qmm_kernel_name(dt, 1, M, N, K, g, bits, tr).decode()
-    assert name(1, 4096, 4096) in ("qmv_stream", "qmv_mma", "qmv_bulk")
-    assert name(16, 14336, 4096) in ("qmv_stream", "qmv_mma", "qmv_bulk")
+    assert name(1, 4096, 4096) == "qmv_rows"
+    assert name(16, 14336, 4096) == "qmv_rows"
     assert name(16, 14336, 4096, bits=3) == "qmv_mma"
     assert name(16, 14336, 4096, dt=_lib.F32) == "qmm_generic"
     assert name(16, 4096, 4096, tr=0) == "qmm_generic"

@@ -56,6 +56,35 @@ def test_repack_checker_matches_the_format_definition(gtype):
         assert np.array_equal(q * sf + bf, want)
 
 
+GGUF_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "gguf_unpack_golden.npz")
+
+
+def _q4_blocks_from_quants(quants, gtype):
+    n = quants.shape[0]
+    head = 2 if gtype == formats.GGUF_Q4_0 else 4
+    blocks = np.zeros((n, head + 16), dtype=np.uint8)
+    blocks[:, 0:2] = np.frombuffer(np.float16(0.25).tobytes(), dtype=np.uint8)
+    blocks[:, head:] = quants
+    return blocks
+
+
+@pytest.mark.parametrize("gtype", (formats.GGUF_Q4_0, formats.GGUF_Q4_1))
+def test_repack_checker_nibble_order_matches_reference_golden(gtype):
+    """The packed words of the checker equal what the reference's own unpack_32_4
+    (mlx/io/gguf_quants.cpp:13-31) produced for the same quant bytes (vectors made by
+    tests/golden/make_golden.py from the reference-compiled binary)."""
+    gold = np.load(GGUF_GOLDEN)
+    wq, _, _ = O.gguf_repack(_q4_blocks_from_quants(gold["quants"], gtype), gtype)
+    assert np.array_equal(wq, gold["unpacked"])
+
+
+@pytest.mark.skipif(not O.have_reference_gguf(), reason="reference-compiled GGUF binary not present")
+def test_repack_checker_nibble_order_matches_reference_live():
+    quants = np.random.default_rng(11).integers(0, 256, (1000, 16), dtype=np.uint8)
+    wq, _, _ = O.gguf_repack(_q4_blocks_from_quants(quants, formats.GGUF_Q4_0), formats.GGUF_Q4_0)
+    assert np.array_equal(wq, O.ref_gguf_unpack(quants))
+
+
 def test_safetensors_round_trip_and_triples(tmp_path):
     rng = np.random.default_rng(1)
     w = (0.02 * rng.standard_normal((64, 256))).astype(np.float32)

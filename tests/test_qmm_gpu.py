@@ -59,20 +59,20 @@ def test_golden_qmm(dtype, g, bits):
 @pytest.mark.parametrize("g", (32, 64, 128))
 @pytest.mark.parametrize("M", (1, 3, 8, 9, 16))
 def test_qmv_all_widths(bits, g, M):
-    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_stream", "qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_rows", "qmv_stream", "qmv_mma", "qmv_bulk"))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 14336, 4096), (7, 67, 256), (2, 8, 128), (16, 1000, 2048),
                                    (5, 28672, 8192), (13, 4104, 4096), (16, 24, 128)])
 def test_qmv_shapes_4bit(M, N, K):
-    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_stream", "qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_rows", "qmv_stream", "qmv_mma", "qmv_bulk"))
 
 
 @pytest.mark.parametrize("M,g", [(1, 64), (2, 32), (4, 128)])
 def test_qmv_stream_is_default_for_large_small_batch(M, g):
     """Large 4-bit matrices with M <= 4 go to the TMA-ring kernel by default (elsewhere it is only
     reachable through B200Q_QMV_IMPL=stream, see the subprocess test below)."""
-    run_case("bf16", M, 28672 - 96, 8192, g, 4, seed=M + g, expect_kernel=("qmv_stream",))
+    run_case("bf16", M, 28672 - 96, 8192, g, 4, seed=M + g, expect_kernel=("qmv_rows", "qmv_stream"))
 
 
 def test_qmv_repeated_calls_reuse_scratch():
@@ -239,7 +239,7 @@ def test_qvm_then_transposed_decode_share_workspace():
     accumulate into the same workspace."""
     for _ in range(2):
         run_case("bf16", 2, 4096, 2048, 64, 4, transpose=False, seed=11, expect_kernel=("qvm",))
-        run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_mma", "qmv_stream"))
+        run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_rows", "qmv_mma", "qmv_stream"))
 
 
 # ---- host-buffer entry point -------------------------------------------------------------------

@@ -21,7 +21,8 @@ pytestmark = pytest.mark.gpu
 P = lambda t: ctypes.c_void_p(t.data_ptr())
 
 
-@pytest.mark.parametrize("M,N,K,g,bits", [(16, 14336, 4096, 64, 4), (1, 4096, 4096, 64, 4), (7, 1000, 1024, 32, 3)])
+@pytest.mark.parametrize("M,N,K,g,bits", [(16, 14336, 4096, 64, 4), (1, 4096, 4096, 64, 4), (7, 1000, 1024, 32, 3),
+                                          (3, 32768, 1024, 64, 4)])  # the last case sits exactly at the built-in array's limit
 def test_static_scratch_matches_workspace_entry_point(M, N, K, g, bits):
     lib = _lib.load()
     dtype = "bf16"
@@ -67,5 +68,7 @@ def test_static_scratch_rejects_oversize_and_bad_arguments():
     assert args(1, 32768 + 16, 4096) == _lib.ERR_UNSUPPORTED
     assert "exceeds the built-in scratch" in _lib.last_error()
     assert args(17, 4096, 4096) == _lib.ERR_UNSUPPORTED
+    assert args(16, 4096, 8192) == _lib.ERR_UNSUPPORTED   # 16 rows of 8192 activations exceed shared memory
+    assert "do not fit in shared memory" in _lib.last_error()
     assert args(4, 4096, 4096, dt=_lib.F32) == _lib.ERR_UNSUPPORTED
     assert args(4, 4096, 4096, g=48) == _lib.ERR_INVALID_ARGUMENT
