@@ -3,26 +3,31 @@
 // Replaces cu::qmv_kernel / the small-M use of cu::qmm_sm80_kernel of the reference
 // (mlx/backend/cuda/quantized/qmm/qmv.cu:84-209, quantized.cpp:106-136).
 //
-// Design (one persistent CTA per SM, 16 warps, no scratch in global memory):
+// Design (one persistent CTA per SM; 16 consumer warps, one loader warp, one reducer warp; no
+// scratch in global memory):
 //  * Every CTA owns a contiguous range of 8-row blocks of W for the WHOLE of K, so no output is
 //    shared between CTAs: no global atomics, no arrival counters, no workspace.
-//  * Packed rows, scales and biases reach shared memory through `cp.async.bulk` (one copy per
-//    row: whole rows are contiguous, so no tensor map and no descriptor fetch is needed), into
-//    a ring of stages of 16 rows each with padded row pitch (bank-conflict-free reads).  All
-//    stages that fit are requested at kernel entry: ~190 KB per SM are in flight from the
-//    first microsecond.  A stage is refilled by whichever warp is last to finish with it.
-//  * K is cut into 16 slices, one per warp.  A warp keeps the x values of its slice in
-//    registers, as mma.sync B fragments in the order the unpack produces weights
-//    (pairs (k, k+4) of every 8 consecutive k), for the whole kernel: x is read from L2 once per
-//    CTA and never touches shared memory.  Long K runs in several phases, x is reloaded per phase.
-//  * Weights are unpacked with shift + lop3 to the bf16 numbers 128+q ("0x4300 | q") and fed to
-//    mma.sync.m16n8k16 as the A operand.  Scales are applied per group to the fp32 group sums,
-//    the "128" offset and the biases come back through two small MMAs against the group sums of
-//    x:  y = sum_g s_g * (sum_k x_k (128 + q_k))  +  sum_g (b_g - 128 s_g) * (sum_k x_k).
-//    8-bit fields are treated as two 4-bit fields against (x, 16 x): same unpack, same rate
-//    per byte.
-//  * The 16 warps leave their fp32 partial tiles in shared memory; the last warp to arrive adds
-//    them in warp order (the result does not depend on timing), converts and stores y.
+//  * A stage is 16 weight rows x one K phase.  The loader warp brings it in with one tiled TMA
+//    load (cp.async.bulk.tensor.3d, box 128 B x 16 rows x up to 32 chunks, 128-byte swizzle) plus
+//    one or two boxes each for the rows' scales and biases: a handful of large copies per stage,
+//    because every bulk-copy instruction costs the SM's copy engine about 60 cycles whatever its
+//    size.  At most `inflight` stages are outstanding, so the first one is not diluted by the rest
+//    and lands early; a ring slot is requested again as soon as all consumers are done with it.
+//  * K is cut into 16 slices, one per consumer warp.  A warp keeps the x values of its slice in
+//    registers for the whole phase, as mma.sync B fragments in the order the unpack produces the
+//    weights: x is read from L2 once per CTA and never touches shared memory.
+//  * Packed words come out of shared memory with ldmatrix (conflict-free on the swizzled tile:
+//    lane (g, t) receives word t of a 16-byte unit of rows g and g+8), are unpacked with
+//    shift + lop3 to the bf16 numbers 128+q ("0x4300 | q") and fed to mma.sync.m16n8k16 as the
+//    A operand.  Scales are applied per group to fp32 group sums; the "128" offset and the biases
+//    come back through two small MMAs against the group sums of x:
+//        y = sum_g s_g * (sum_k x_k (128 + q_k))  +  sum_g (b_g - 128 s_g) * (sum_k x_k).
+//    8-bit fields are treated as two 4-bit fields against (x, 16 x): same unpack, same rate per
+//    byte.  Four independent accumulation chains per warp hide the mma.sync latency.
+//  * The consumer warps leave fp32 partial tiles in shared memory; the reducer warp adds them in
+//    warp order (the result does not depend on timing), converts and stores y.
+#include <cuda.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -37,10 +42,30 @@ using tc::mbar_expect_tx;
 using tc::mbar_wait;
 using tc::smem_u32;
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
-constexpr int kPartialBufs = 2;
+constexpr int kConsumers = 16;                   // warps that multiply; one K slice each
+// Registers are handed out per group of four warps: the loader and the reducer warp come with two
+// idle companions, and the two kinds of warps re-balance their register budgets at entry.
+constexpr int kThreads = (kConsumers + 4) * 32;
+constexpr int kRegsConsumer = 112, kRegsService = 32;
+// setmaxnreg only moves registers inside what the block was launched with (96 per thread at this
+// block size): a request beyond that pool would wait forever.
+static_assert(kRegsConsumer * kConsumers * 32 + kRegsService * 4 * 32 <= 96 * kThreads,
+              "register budgets exceed the launch allocation");
+constexpr int kPartialBufs = 2;                  // fp32 partial tiles of the stages being reduced
 constexpr size_t kSmemLimit = 227 * 1024;
+
+// Clock marks for tuning builds only (-DB200Q_ROWS_PROFILE): cycles since kernel entry per CTA and
+// warp, in a buffer of their own that a test harness reads back with cudaMemcpyFromSymbol.
+#ifdef B200Q_ROWS_PROFILE
+__device__ uint32_t g_rows_prof[160][kConsumers + 4][32];
+#define RP_MARK(i)                                                                            \
+  do {                                                                                        \
+    if (lane == 0 && (i) < 32 && blockIdx.x < 160)                                            \
+      g_rows_prof[blockIdx.x][warp][(i)] = (uint32_t)(clock64() - rp_entry);                  \
+  } while (0)
+#else
+#define RP_MARK(i)
+#endif
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t d;
@@ -59,64 +84,59 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+// Four 8x8 matrices of 16-bit elements; lane l supplies the address of row l%8 of matrix l/8 and
+// receives, from matrix m, the 32-bit word (l%4) of row l/4.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr)
                : "memory");
 }
-__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts_f4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ uint4 ldg_nc_u128(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+__device__ __forceinline__ uint2 ldg_nc_u64(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+__device__ __forceinline__ float sum_bf16x2(uint32_t v) { return bf16lo(v) + bf16hi(v); }
 
-// Compile-time shape of one (bits, group size, token tiles) instantiation.
+__host__ __device__ constexpr int cmin(int a, int b) { return a < b ? a : b; }
+__host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
+
+// Compile-time shape of one (bits, group size, token tiles) instantiation.  A "unit" is 16 packed
+// bytes of one row (what one ldmatrix row holds); lane t of a quad owns word t of every unit.
 template <int BITS, int G, int MT>
 struct Cfg {
   static_assert(BITS == 2 || BITS == 4 || BITS == 8, "field widths handled by this kernel");
-  static constexpr int GB = G * BITS / 8;            // packed bytes of one group of one row
-  static constexpr int LB = GB / 4;                  // ... of which one lane of a quad reads
-  static constexpr int KBLK = BITS == 8 ? 4 : 8;     // k values per unpack block (four bf16 pairs)
-  static constexpr int NBLK = (G / 4) / KBLK;        // blocks per lane and group
-  static constexpr int WORDS = LB >= 4 ? LB / 4 : 1; // registers holding the lane's packed bytes
-  static constexpr int XG = MT * NBLK * 4;           // x registers per group
-  static constexpr int NGW_RAW = 64 / XG;            // groups per warp and phase: 64 registers of x
-  static constexpr int NGW = NGW_RAW > 8 ? 8 : (NGW_RAW < 1 ? 1 : NGW_RAW);
-  // Row pitch padding (bytes mod 128) that makes the quad-per-row reads conflict-free.
-  static constexpr int PAD = LB == 8 ? 32 : (LB == 16 ? 64 : 16);
+  static constexpr int GB = G * BITS / 8;                  // packed bytes of one group of one row
+  static_assert(GB >= 16, "a group must fill at least one 16-byte unit");
+  static constexpr int UG = GB / 16;                       // units per group
+  static constexpr int KW = BITS == 8 ? 4 : (BITS == 4 ? 8 : 16);   // k values per 32-bit word
+  static constexpr int NB = BITS == 2 ? 2 : 1;             // unpack blocks (four bf16 pairs) per word
+  static constexpr int XU = MT * NB * 4;                   // x registers per unit
+  static constexpr int UW = cmax(UG, cmin(64 / XU, 8 * UG));   // units per warp and phase (64 x registers, 8 groups)
+  static constexpr int NGW = UW / UG;                      // groups per warp and phase
 };
 
 struct RowsParams {
   const __nv_bfloat16* x;
-  const unsigned char* wq;
-  const unsigned char* scales;
-  const unsigned char* biases;
   __nv_bfloat16* y[kMaxPeers];
   int n_out;
   long long ld, col0;
@@ -124,71 +144,59 @@ struct RowsParams {
   int nblk8;            // ceil(N / 8)
   int groups;           // K / G
   int nph, gph;         // phases over K, groups per (full) phase
+  int nch, nsb;         // 128-byte chunks of packed bytes / of scales per row and phase
   int nst;              // ring stages
-  uint32_t rs, srs;     // shared-memory pitch of a packed row chunk / a scale row chunk
-  uint32_t slot_bytes;  // 16 * rs + 32 * srs
-  uint32_t off_slots, off_pbuf, off_tile, off_tileph;
-  long long row_bytes;  // K * BITS / 8
-  long long srow_bytes; // groups * 2
+  uint32_t slot_bytes;  // (nch + 2 * nsb) * 2048
+  uint32_t off_slots, off_tile, off_pbuf;
+  int inflight;         // stages requested but not yet landed, at most
   uint32_t* status;     // may be null
   int early;            // weights, scales and biases may be read before the previous kernel ended
 };
 
-// Unpacks block `blk` of the lane's packed bytes into four bf16x2 registers (128+q_i, 128+q_{i+4}).
+// Unpacks block `blk` of a packed word into four bf16x2 registers (128+q_i, 128+q_{i+4}).
 template <int BITS>
-__device__ __forceinline__ void unpack_block(const uint32_t* w, int blk, uint32_t (&P)[4]) {
+__device__ __forceinline__ void unpack_block(uint32_t w, int blk, uint32_t (&P)[4]) {
   constexpr uint32_t kMagic = 0x43004300u;
   if constexpr (BITS == 4 || BITS == 8) {
-    const uint32_t v = w[blk];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) P[i] = lop3_and_or(v >> (4 * i), 0x000F000Fu, kMagic);
+    for (int i = 0; i < 4; ++i) P[i] = lop3_and_or(w >> (4 * i), 0x000F000Fu, kMagic);
   } else {
     // 16 fields per word; a block is one half word: spread its two bytes to bits 0-7 / 16-23
-    const uint32_t v = __byte_perm(w[blk >> 1], 0u, (blk & 1) ? 0x4342 : 0x4140);
+    const uint32_t v = __byte_perm(w, 0u, blk ? 0x4342 : 0x4140);
 #pragma unroll
     for (int i = 0; i < 4; ++i) P[i] = lop3_and_or(v >> (2 * i), 0x00030003u, kMagic);
   }
 }
 
-template <int LB>
-__device__ __forceinline__ void lds_lane(uint32_t addr, uint32_t* w) {
-  if constexpr (LB == 2) {
-    w[0] = lds_u16(addr);
-  } else if constexpr (LB == 4) {
-    w[0] = lds_u32(addr);
-  } else if constexpr (LB == 8) {
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr));
-  } else {
-#pragma unroll
-    for (int i = 0; i < LB / 16; ++i)
-      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
-                   : "r"(addr + 16 * i));
-  }
-}
-
 template <int BITS, int G, int MT>
-__global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                const __grid_constant__ CUtensorMap map_b, const RowsParams p) {
   using C = Cfg<BITS, G, MT>;
-  constexpr int NGW = C::NGW, NBLK = C::NBLK, GB = C::GB, LB = C::LB;
-  extern __shared__ __align__(128) unsigned char smem[];
-  // header: [0, 8*nst) full barriers | 256: arrive counters | 320: partial-buffer epochs | 384: abort
+  constexpr int NGW = C::NGW, NB = C::NB, UG = C::UG, UW = C::UW, KW = C::KW;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  // header: [0, 128) "stage landed" barriers | [128, 256) "stage consumed" barriers |
+  //         [256, 288) "partial buffer free" barriers | 320: abort flag
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar0 = smem_base;
-  volatile int* arrive = reinterpret_cast<volatile int*>(smem + 256);
-  volatile int* pb_done = reinterpret_cast<volatile int*>(smem + 320);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 384);
-  volatile int* tile_ph = reinterpret_cast<volatile int*>(smem + p.off_tileph);
+  const uint32_t full0 = smem_base, done0 = smem_base + 128, pfree0 = smem_base + 256;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 320);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  {
-    // The first mma.sync of a kernel is slow (the tensor pipe wakes up): issue one now.
-    float d0, d1, d2, d3;
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
-                 : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
+#ifdef B200Q_ROWS_PROFILE
+  const long long rp_entry = clock64();
+  if (lane == 0 && blockIdx.x < 160) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    g_rows_prof[blockIdx.x][warp][31] = (uint32_t)gt;
   }
+#endif
   asm volatile("griddepcontrol.launch_dependents;");
+  if (tid == kConsumers * 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_s) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
 
   const int G_ = gridDim.x;
   const int b0 = (int)((long long)blockIdx.x * p.nblk8 / G_);
@@ -199,95 +207,175 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams 
   const int nst = p.nst;
 
   if (tid == 0) {
-    for (int i = 0; i < nst; ++i) mbar_init(bar0 + 8 * i, 1);
-    for (int i = 0; i < 16; ++i) arrive[i] = 0;
-    for (int i = 0; i < kPartialBufs; ++i) pb_done[i] = 0;
+    for (int i = 0; i < nst; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(done0 + 8 * i, kConsumers);
+    }
+    for (int i = 0; i < kPartialBufs; ++i) mbar_init(pfree0 + 8 * i, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (p.nph > 1)
-    for (int i = tid; i < nrg; i += kThreads) tile_ph[i] = 0;
   __syncthreads();
+  RP_MARK(1);
 
-  // ---- producer side: one warp requests one stage ------------------------------------
-  auto issue_stage = [&](int s) {
-    const int ph = s / nrg, rg = s - ph * nrg;
-    const int slot = s % nst;
-    const int gp = min(p.gph, p.groups - ph * p.gph);
-    const uint32_t wbytes = (uint32_t)gp * GB, sbytes = (uint32_t)gp * 2;
-    const int row0 = (b0 + 2 * rg) * 8;
-    const int nrows = min(16, row_end - row0);
-    const uint32_t bar = bar0 + 8 * slot;
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)nrows * (wbytes + 2 * sbytes));
-    __syncwarp();
-    const uint32_t slot_base = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
-    const int r = lane & 15;
-    if (r < nrows) {
-      if (lane < 16) {
-        bulk_g2s(slot_base + r * p.rs, p.wq + (long long)(row0 + r) * p.row_bytes + (long long)ph * p.gph * GB, wbytes, bar);
-      } else {
-        const long long so = (long long)(row0 + r) * p.srow_bytes + (long long)ph * p.gph * 2;
-        bulk_g2s(slot_base + 16 * p.rs + r * p.srs, p.scales + so, sbytes, bar);
-        bulk_g2s(slot_base + 16 * p.rs + 16 * p.srs + r * p.srs, p.biases + so, sbytes, bar);
+  if (warp >= kConsumers) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
+    if (warp == kConsumers) {
+      // ================================= loader warp ==========================================
+      // Without the caller's promise the weights may have been written by the previous kernel.
+      if (!p.early) asm volatile("griddepcontrol.wait;" ::: "memory");
+      RP_MARK(2);
+      if (lane == 0) {
+        const uint32_t stage_bytes = p.slot_bytes;
+        const int chunks_per_phase = p.gph * C::GB / 128;
+        int landed = 0, iph = 0, irg = 0;
+        for (int s = 0; s < total; ++s) {
+          const int slot = s % nst;
+          // slot free: all consumer warps arrived for the stage that used it last
+          if (s >= nst && !mbar_wait(done0 + 8 * slot, ((s - nst) / nst) & 1, abort_flag)) break;
+          // at most p.inflight stages outstanding
+          while (landed < s && tc::mbar_try(full0 + 8 * (landed % nst), (landed / nst) & 1)) ++landed;
+          if (s - landed >= p.inflight) {
+            const int w = s - p.inflight;
+            if (!mbar_wait(full0 + 8 * (w % nst), (w / nst) & 1, abort_flag)) break;
+            landed = w + 1;
+          }
+          const int row0 = (b0 + 2 * irg) * 8;
+          const uint32_t bar = full0 + 8 * slot;
+          const uint32_t dst = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
+          // rows past N and chunks past K are zero-filled by the copy engine and still counted
+          mbar_expect_tx(bar, stage_bytes);
+          tma_load_3d(dst, &map_w, 0, row0, iph * chunks_per_phase, bar);
+          for (int i = 0; i < p.nsb; ++i) {
+            tc::tma_load_2d(dst + (p.nch + i) * 2048, &map_s, iph * p.gph * 2 + 128 * i, row0, bar);
+            tc::tma_load_2d(dst + (p.nch + p.nsb + i) * 2048, &map_b, iph * p.gph * 2 + 128 * i, row0, bar);
+          }
+#ifdef B200Q_ROWS_PROFILE
+          if (5 + s < 30 && blockIdx.x < 160) g_rows_prof[blockIdx.x][warp][5 + s] = (uint32_t)(clock64() - rp_entry);
+#endif
+          if (++irg == nrg) { irg = 0; ++iph; }
+        }
       }
+      RP_MARK(30);
+    } else if (warp == kConsumers + 1) {
+      // ================================= reducer warp =========================================
+      // Adds the consumer warps' partial tiles of a finished stage in warp order, frees the
+      // partial buffer, and stores y (or keeps running sums while K is walked in phases).
+      asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be in use by the previous kernel
+      int rph = 0, rrg = 0;
+      for (int red = 0; red < total; ++red) {
+        if (!mbar_wait(done0 + 8 * (red % nst), (red / nst) & 1, abort_flag)) break;
+        RP_MARK(5 + 2 * red);
+        const int gp = min(p.gph, p.groups - rph * p.gph);
+        const int nact = gp < kConsumers ? gp : kConsumers;
+        const int pbi = red % kPartialBufs;
+        const float4* pb = reinterpret_cast<const float4*>(smem + p.off_pbuf + (size_t)pbi * (kConsumers * MT * 512)) + lane;
+        float sum[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          int w = 0;
+          for (; w + 4 <= nact; w += 4) {   // four independent loads, then the additions in warp order
+            const float4 v0 = pb[((w + 0) * MT + mt) * 32], v1 = pb[((w + 1) * MT + mt) * 32];
+            const float4 v2 = pb[((w + 2) * MT + mt) * 32], v3 = pb[((w + 3) * MT + mt) * 32];
+            acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+            acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+            acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+            acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
+          }
+          for (; w < nact; ++w) {
+            const float4 v = pb[(w * MT + mt) * 32];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          sum[mt][0] = acc.x; sum[mt][1] = acc.y; sum[mt][2] = acc.z; sum[mt][3] = acc.w;
+        }
+        __syncwarp();   // every lane holds its sums: the partial buffer may be written again
+        if (lane == 0) tc::mbar_arrive(pfree0 + 8 * pbi);
+        bool final_phase = true;
+        if (p.nph > 1) {   // long K: running sums of this CTA's rows, touched by this warp only
+          float4* tl = reinterpret_cast<float4*>(smem + p.off_tile + (size_t)rrg * (MT * 512)) + lane;
+          final_phase = rph == p.nph - 1;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            if (rph > 0) {
+              const float4 v = tl[mt * 32];
+              sum[mt][0] += v.x; sum[mt][1] += v.y; sum[mt][2] += v.z; sum[mt][3] += v.w;
+            }
+            if (!final_phase) tl[mt * 32] = make_float4(sum[mt][0], sum[mt][1], sum[mt][2], sum[mt][3]);
+          }
+        }
+        if (final_phase) {
+          const int row0 = (b0 + 2 * rrg) * 8;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int row = row0 + g + (c >> 1) * 8;
+              const int tok = mt * 8 + 2 * t + (c & 1);
+              if (row < row_end && tok < p.M) {
+                const __nv_bfloat16 o = __float2bfloat16_rn(sum[mt][c]);
+                const long long at = (long long)tok * p.ld + p.col0 + row;
+                p.y[0][at] = o;
+                for (int q = 1; q < p.n_out; ++q) p.y[q][at] = o;
+              }
+            }
+          }
+        }
+        if (++rrg == nrg) { rrg = 0; ++rph; }
+        RP_MARK(6 + 2 * red);
+      }
+      RP_MARK(30);
     }
-  };
+    if (*abort_flag && lane == 0 && warp == kConsumers && p.status) atomicMax(&p.status[0], 7u);
+    return;
+  }
 
-  if (p.early)
-    for (int s = warp; s < min(nst, total); s += kWarps) issue_stage(s);
-  // Everything the previous kernel of the stream may still produce (x) or use (y) is touched only
-  // after this point.  Without the launch attribute the instruction returns at once.
+  // ================================= consumer warps ===========================================
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsConsumer));
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (!p.early)
-    for (int s = warp; s < min(nst, total); s += kWarps) issue_stage(s);
-
-  // ---- per-phase state of this warp -----------------------------------------------------
-  uint32_t X[NGW][NBLK][MT][4];   // B fragments of this warp's K slice
+  RP_MARK(2);
+  uint32_t X[UW][NB][MT][4];      // B fragments of this warp's K slice
   uint32_t sx_hi[MT], sx_lo[MT];  // group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)
-  int cnt = 0, g0 = 0, nact = 0;
+  int cnt = 0, g0 = 0;
   int ph = 0, rg = 0, slot = 0, use = 0, pbi = 0, pbe = 0;
 
   auto setup_phase = [&]() {
     const int gp = min(p.gph, p.groups - ph * p.gph);
-    const int base = gp / kWarps, rem = gp - base * kWarps;
+    const int base = gp / kConsumers, rem = gp - base * kConsumers;
     cnt = base + (warp < rem ? 1 : 0);
     g0 = warp * base + min(warp, rem);
-    nact = gp < kWarps ? gp : kWarps;
     float sx[NGW][MT];
 #pragma unroll
-    for (int gi = 0; gi < NGW; ++gi) {
+    for (int j = 0; j < NGW; ++j)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) sx[j][mt] = 0.0f;
+    // unit i of the slice: 4 * KW consecutive k, of which this lane owns KW starting at t * KW
+    const long long k0 = (long long)(ph * p.gph + g0) * G + t * KW;
+#pragma unroll
+    for (int i = 0; i < UW; ++i) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        sx[gi][mt] = 0.0f;
         const int tok = mt * 8 + g;
-        const bool live = gi < cnt && tok < p.M;
-        const __nv_bfloat16* xp = p.x + (long long)tok * p.K + (long long)(ph * p.gph + g0 + gi) * G + t * (G / 4);
+        const bool live = i < cnt * UG && tok < p.M;
+        const __nv_bfloat16* xp = p.x + (long long)tok * p.K + k0 + i * (4 * KW);
         if constexpr (BITS == 8) {
-          // two blocks of 4 k per 16-byte load; pairs (x0,x2), 16(x0,x2), (x1,x3), 16(x1,x3)
-#pragma unroll
-          for (int j = 0; j < NBLK / 2; ++j) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (live) v = ldg_nc_u128(xp + 8 * j);
-            sx[gi][mt] += (bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y)) + (bf16lo(v.z) + bf16hi(v.z)) +
-                          (bf16lo(v.w) + bf16hi(v.w));
-            const uint32_t a = __byte_perm(v.x, v.y, 0x5410), b = __byte_perm(v.x, v.y, 0x7632);
-            const uint32_t c = __byte_perm(v.z, v.w, 0x5410), d = __byte_perm(v.z, v.w, 0x7632);
-            X[gi][2 * j][mt][0] = a; X[gi][2 * j][mt][1] = mul_bf16x2(a, 0x41804180u);
-            X[gi][2 * j][mt][2] = b; X[gi][2 * j][mt][3] = mul_bf16x2(b, 0x41804180u);
-            X[gi][2 * j + 1][mt][0] = c; X[gi][2 * j + 1][mt][1] = mul_bf16x2(c, 0x41804180u);
-            X[gi][2 * j + 1][mt][2] = d; X[gi][2 * j + 1][mt][3] = mul_bf16x2(d, 0x41804180u);
-          }
+          // one word = 4 k; pairs (x0,x2), 16(x0,x2), (x1,x3), 16(x1,x3)
+          uint2 v = make_uint2(0, 0);
+          if (live) v = ldg_nc_u64(xp);
+          sx[i / UG][mt] += sum_bf16x2(v.x) + sum_bf16x2(v.y);
+          const uint32_t a = __byte_perm(v.x, v.y, 0x5410), b = __byte_perm(v.x, v.y, 0x7632);
+          X[i][0][mt][0] = a; X[i][0][mt][1] = mul_bf16x2(a, 0x41804180u);
+          X[i][0][mt][2] = b; X[i][0][mt][3] = mul_bf16x2(b, 0x41804180u);
         } else {
 #pragma unroll
-          for (int j = 0; j < NBLK; ++j) {
+          for (int nb = 0; nb < NB; ++nb) {
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (live) v = ldg_nc_u128(xp + 8 * j);
-            sx[gi][mt] += (bf16lo(v.x) + bf16hi(v.x)) + (bf16lo(v.y) + bf16hi(v.y)) + (bf16lo(v.z) + bf16hi(v.z)) +
-                          (bf16lo(v.w) + bf16hi(v.w));
-            X[gi][j][mt][0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
-            X[gi][j][mt][1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
-            X[gi][j][mt][2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
-            X[gi][j][mt][3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
+            if (live) v = ldg_nc_u128(xp + 8 * nb);
+            sx[i / UG][mt] += (sum_bf16x2(v.x) + sum_bf16x2(v.y)) + (sum_bf16x2(v.z) + sum_bf16x2(v.w));
+            X[i][nb][mt][0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
+            X[i][nb][mt][1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
+            X[i][nb][mt][2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
+            X[i][nb][mt][3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
           }
         }
       }
@@ -297,12 +385,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams 
     for (int mt = 0; mt < MT; ++mt) {
       float e0 = 0.0f, e1 = 0.0f;
 #pragma unroll
-      for (int gi = 0; gi < NGW; ++gi) {
-        float v = sx[gi][mt];
+      for (int j = 0; j < NGW; ++j) {
+        float v = sx[j][mt];
         v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
         v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-        if ((gi >> 1) == t) {
-          if (gi & 1) e1 = v; else e0 = v;
+        if ((j >> 1) == t) {
+          if (j & 1) e1 = v; else e0 = v;
         }
       }
       const uint32_t hi = pack_bf16x2(e0, e1);
@@ -311,65 +399,122 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams 
     }
   };
   setup_phase();
+  {
+    // The first mma.sync of a kernel is slow (the tensor pipe wakes up): issue one now, while the
+    // first stage is in flight anyway.  Its result is never used.
+    float d0, d1, d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%4,%4}, {%5,%5,%5,%5};"
+                 : "=f"(d0), "=f"(d1), "=f"(d2), "=f"(d3) : "r"(0u), "f"(0.0f));
+  }
+  RP_MARK(4);
 
-  // ---- main loop over stages -------------------------------------------------------------
+  // ldmatrix roles of this lane: matrix m = lane / 8 covers rows (m & 1) * 8 .. +7 of unit (m >> 1)
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_unit = lane >> 4, lm_x = lane & 7;
   for (int s = 0; s < total; ++s) {
+    if (!mbar_wait(full0 + 8 * slot, use & 1, abort_flag)) break;
+    RP_MARK(5 + 3 * s);
     if (cnt > 0) {
-      const uint32_t slot_base = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
-      if (!mbar_wait(bar0 + 8 * slot, use & 1, abort_flag)) break;
+      const uint32_t sb = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
+      const unsigned char* sbp = smem + p.off_slots + (size_t)slot * p.slot_bytes;
+      // scale / bias of (row g, group J of the phase): 128-byte rows, 16-byte units xor-ed with the
+      // row number mod 8; the same entry of row g + 8 is 1024 bytes (512 elements) further on
+      auto sc_ptr = [&](int tile0, int J) -> const unsigned short* {
+        const int b = 2 * J;
+        return reinterpret_cast<const unsigned short*>(sbp + (size_t)(tile0 + (b >> 7)) * 2048 + g * 128 +
+                                                        ((((b >> 4) & 7) ^ g) << 4) + (b & 15));
+      };
       float out[MT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) out[mt][c] = 0.0f;
-      const uint32_t w_lo = slot_base + g * p.rs + g0 * GB + t * LB;
-      const uint32_t w_hi = w_lo + 8 * p.rs;
-      const uint32_t sc_lo = slot_base + 16 * p.rs + g * p.srs + g0 * 2;
-      const uint32_t sc_hi = sc_lo + 8 * p.srs;
+      // mma.sync results come back after ~100 cycles: keep four independent accumulation chains
+      // going per warp (PAIR groups at a time, each group's k steps dealt round-robin to SPLIT
+      // accumulators, MT token tiles).
+      constexpr int PAIR = NGW >= 2 ? 2 : 1;
+      constexpr int STEPS = UG * NB * 2;   // mma k steps per group
+      constexpr int SPLIT = cmax(1, cmin(4 / (MT * PAIR), STEPS));
+      constexpr int PU = PAIR * UG;        // units per iteration (even)
+      static_assert(PU % 2 == 0, "units are fetched two at a time");
+      const int u0 = g0 * UG;              // first unit of this warp in the stage
 #pragma unroll
-      for (int gi = 0; gi < NGW; ++gi) {
-        if (gi < cnt) {
-          uint32_t wl[C::WORDS], wh[C::WORDS];
-          lds_lane<LB>(w_lo + gi * GB, wl);
-          lds_lane<LB>(w_hi + gi * GB, wh);
-          const float s_l = __uint_as_float(lds_u16(sc_lo + gi * 2) << 16);
-          const float s_h = __uint_as_float(lds_u16(sc_hi + gi * 2) << 16);
-          float acc[MT][4];
+      for (int gq = 0; gq < NGW; gq += PAIR) {
+        if (gq < cnt) {
+          // packed words: lane (g, t) gets word t of unit i for rows g (wl) and g + 8 (wh)
+          uint32_t wl[PU], wh[PU];
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
+          for (int i = 0; i < PU; i += 2) {
+            const int U = u0 + gq * UG + i + lm_unit;
+            const uint32_t addr = sb + (uint32_t)(U >> 3) * 2048 + lm_row * 128 + (((U & 7) ^ lm_x) << 4);
+            ldmatrix_x4(addr, wl[i], wh[i], wl[i + 1], wh[i + 1]);
+          }
+          float s_l[PAIR], s_h[PAIR];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[mt][c] = 0.0f;
+          for (int u = 0; u < PAIR; ++u) {
+            // a group past the warp's share multiplies a neighbour's packed bytes (finite after the
+            // unpack) with x registers that are zero; its scale is forced to zero
+            const bool live = gq + u < cnt;
+            const unsigned short* sp = sc_ptr(p.nch, g0 + gq + u);
+            s_l[u] = live ? __uint_as_float((uint32_t)sp[0] << 16) : 0.0f;
+            s_h[u] = live ? __uint_as_float((uint32_t)sp[512] << 16) : 0.0f;
+          }
+          float acc[PAIR][MT][SPLIT][4];
 #pragma unroll
-          for (int j = 0; j < NBLK; ++j) {
-            uint32_t Pl[4], Ph[4];
-            unpack_block<BITS>(wl, j, Pl);
-            unpack_block<BITS>(wh, j, Ph);
+          for (int u = 0; u < PAIR; ++u)
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-              for (int mt = 0; mt < MT; ++mt)
-                mma_bf16(acc[mt], Pl[2 * h], Ph[2 * h], Pl[2 * h + 1], Ph[2 * h + 1], X[gi][j][mt][2 * h],
-                         X[gi][j][mt][2 * h + 1]);
+              for (int q = 0; q < SPLIT; ++q)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[u][mt][q][c] = 0.0f;
+#pragma unroll
+          for (int iu = 0; iu < UG; ++iu) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              uint32_t Pl[PAIR][4], Ph[PAIR][4];
+#pragma unroll
+              for (int u = 0; u < PAIR; ++u) {
+                unpack_block<BITS>(wl[u * UG + iu], nb, Pl[u]);
+                unpack_block<BITS>(wh[u * UG + iu], nb, Ph[u]);
+              }
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int u = 0; u < PAIR; ++u)
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt)
+                    mma_bf16(acc[u][mt][((iu * NB + nb) * 2 + h) % SPLIT], Pl[u][2 * h], Ph[u][2 * h], Pl[u][2 * h + 1],
+                             Ph[u][2 * h + 1], X[(gq + u) * UG + iu][nb][mt][2 * h], X[(gq + u) * UG + iu][nb][mt][2 * h + 1]);
+            }
           }
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            out[mt][0] = fmaf(s_l, acc[mt][0], out[mt][0]);
-            out[mt][1] = fmaf(s_l, acc[mt][1], out[mt][1]);
-            out[mt][2] = fmaf(s_h, acc[mt][2], out[mt][2]);
-            out[mt][3] = fmaf(s_h, acc[mt][3], out[mt][3]);
-          }
+          for (int u = 0; u < PAIR; ++u)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+              for (int q = 1; q < SPLIT; ++q)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[u][mt][0][c] += acc[u][mt][q][c];
+              out[mt][0] = fmaf(s_l[u], acc[u][mt][0][0], out[mt][0]);
+              out[mt][1] = fmaf(s_l[u], acc[u][mt][0][1], out[mt][1]);
+              out[mt][2] = fmaf(s_h[u], acc[u][mt][0][2], out[mt][2]);
+              out[mt][3] = fmaf(s_h[u], acc[u][mt][0][3], out[mt][3]);
+            }
         }
       }
       // biases and the unpack offset: (b_g - OFFSET * s_g) * sum_k x_k, k slots 2t, 2t+1 (hi) / +8 (lo)
       {
         uint32_t bl = 0, bh = 0, sl = 0, sh = 0;
         if (2 * t < cnt) {
-          const uint32_t bi_lo = sc_lo + 16 * p.srs, bi_hi = sc_hi + 16 * p.srs;
           const bool two = 2 * t + 1 < cnt;
-          bl = lds_u16(bi_lo + 4 * t) | (two ? lds_u16(bi_lo + 4 * t + 2) << 16 : 0u);
-          bh = lds_u16(bi_hi + 4 * t) | (two ? lds_u16(bi_hi + 4 * t + 2) << 16 : 0u);
-          sl = lds_u16(sc_lo + 4 * t) | (two ? lds_u16(sc_lo + 4 * t + 2) << 16 : 0u);
-          sh = lds_u16(sc_hi + 4 * t) | (two ? lds_u16(sc_hi + 4 * t + 2) << 16 : 0u);
+          const unsigned short* ps0 = sc_ptr(p.nch, g0 + 2 * t);
+          const unsigned short* pb0 = sc_ptr(p.nch + p.nsb, g0 + 2 * t);
+          const unsigned short* ps1 = sc_ptr(p.nch, g0 + 2 * t + (two ? 1 : 0));
+          const unsigned short* pb1 = sc_ptr(p.nch + p.nsb, g0 + 2 * t + (two ? 1 : 0));
+          sl = ps0[0] | (two ? (uint32_t)ps1[0] << 16 : 0u);
+          sh = ps0[512] | (two ? (uint32_t)ps1[512] << 16 : 0u);
+          bl = pb0[0] | (two ? (uint32_t)pb1[0] << 16 : 0u);
+          bh = pb0[512] | (two ? (uint32_t)pb1[512] << 16 : 0u);
         }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -379,100 +524,16 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams 
             mma_bf16(out[mt], sl, sh, sl, sh, mul_bf16x2(sx_hi[mt], 0xC500C500u), mul_bf16x2(sx_lo[mt], 0xC500C500u));
         }
       }
-      // hand the partial tile over
-      if (pbe > 0 && lane == 0) {
-        uint32_t spins = 0;
-        while (pb_done[pbi] < pbe) {
-          if (++spins > tc::kSpinLimit) { *abort_flag = 1; break; }
-          __nanosleep(20);
-        }
-      }
-      __syncwarp();
-      if (*abort_flag) break;
-      const uint32_t pb = smem_base + p.off_pbuf + (uint32_t)pbi * (kWarps * MT * 512);
+      RP_MARK(6 + 3 * s);
+      // the partial buffer of this stage was read by the reducer kPartialBufs stages ago
+      if (pbe > 0 && !mbar_wait(pfree0 + 8 * pbi, (pbe - 1) & 1, abort_flag)) break;
+      float4* pb = reinterpret_cast<float4*>(smem + p.off_pbuf + (size_t)pbi * (kConsumers * MT * 512)) + (warp * MT) * 32 + lane;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-        sts_f4(pb + (warp * MT + mt) * 512 + lane * 16, out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
-      __syncwarp();
-      int last = 0;
-      if (lane == 0) {
-        __threadfence_block();
-        const int old = atomicAdd(const_cast<int*>(&arrive[slot]), 1);
-        last = (old == nact - 1);
-      }
-      last = __shfl_sync(0xFFFFFFFFu, last, 0);
-      if (last) {
-        __threadfence_block();
-        float sum[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) sum[mt][c] = 0.0f;
-        for (int w = 0; w < nact; ++w) {
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const float4 v = lds_f4(pb + (w * MT + mt) * 512 + lane * 16);
-            sum[mt][0] += v.x; sum[mt][1] += v.y; sum[mt][2] += v.z; sum[mt][3] += v.w;
-          }
-        }
-        __syncwarp();
-        if (lane == 0) {
-          arrive[slot] = 0;
-          __threadfence_block();
-          pb_done[pbi] = pbe + 1;
-        }
-        bool final_phase = true;
-        if (p.nph > 1) {
-          const uint32_t tl = smem_base + p.off_tile + (uint32_t)rg * (MT * 512);
-          if (ph > 0) {
-            if (lane == 0) {
-              uint32_t spins = 0;
-              while (tile_ph[rg] < ph) {
-                if (++spins > tc::kSpinLimit) { *abort_flag = 1; break; }
-                __nanosleep(20);
-              }
-            }
-            __syncwarp();
-            __threadfence_block();
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              const float4 v = lds_f4(tl + mt * 512 + lane * 16);
-              sum[mt][0] += v.x; sum[mt][1] += v.y; sum[mt][2] += v.z; sum[mt][3] += v.w;
-            }
-          }
-          final_phase = ph == p.nph - 1;
-          if (!final_phase) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) sts_f4(tl + mt * 512 + lane * 16, sum[mt][0], sum[mt][1], sum[mt][2], sum[mt][3]);
-            __syncwarp();
-            if (lane == 0) {
-              __threadfence_block();
-              tile_ph[rg] = ph + 1;
-            }
-          }
-        }
-        if (final_phase) {
-          const int row0 = (b0 + 2 * rg) * 8;
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int row = row0 + g + (c >> 1) * 8;
-              const int tok = mt * 8 + 2 * t + (c & 1);
-              if (row < row_end && tok < p.M) {
-                const __nv_bfloat16 o = __float2bfloat16_rn(sum[mt][c]);
-                for (int q = 0; q < p.n_out; ++q) p.y[q][(long long)tok * p.ld + p.col0 + row] = o;
-              }
-            }
-          }
-        }
-        if (s + nst < total) {
-          // the refill overwrites bytes every warp has finished reading (they all arrived above)
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          issue_stage(s + nst);
-        }
-      }
+      for (int mt = 0; mt < MT; ++mt) pb[mt * 32] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
     }
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(done0 + 8 * slot);   // release: the partial tile is visible to the reducer
+    RP_MARK(7 + 3 * s);
     // advance to the next stage
     if (++slot == nst) { slot = 0; ++use; }
     if (++pbi == kPartialBufs) { pbi = 0; ++pbe; }
@@ -482,7 +543,25 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_rows_kernel(const RowsParams 
       if (ph < p.nph) setup_phase();
     }
   }
-  if (*abort_flag && tid == 0 && p.status) atomicMax(&p.status[0], 7u);
+  RP_MARK(30);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn rows_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
 }
 
 struct RowsPlan {
@@ -509,26 +588,26 @@ bool fill_plan(const QmmArgs& a, RowsPlan& pl) {
   using C = Cfg<BITS, G, MT>;
   RowsParams& p = pl.prm;
   const int groups = (int)(a.K / G);
-  const int cap = kWarps * C::NGW;
+  const int cap = kConsumers * C::NGW;
   p.nph = (groups + cap - 1) / cap;
-  p.gph = ((groups + p.nph - 1) / p.nph + 7) / 8 * 8;
+  p.gph = ((groups + p.nph - 1) / p.nph + 7) / 8 * 8;   // whole 16-byte pieces of scales, whole 128-byte chunks of W
   if (p.gph > cap) return false;
   p.groups = groups;
-  p.rs = (uint32_t)((p.gph * C::GB + 127) / 128 * 128 + C::PAD);
-  p.srs = (uint32_t)((p.gph * 2 + 127) / 128 * 128 + 16);
-  p.slot_bytes = 16 * p.rs + 32 * p.srs;
+  p.nch = (p.gph * C::GB + 127) / 128;
+  p.nsb = (p.gph * 2 + 127) / 128;
+  if (p.nch > 256) return false;
+  p.slot_bytes = (uint32_t)(p.nch + 2 * p.nsb) * 2048;
   p.nblk8 = (int)((a.N + 7) / 8);
   const int sms = sm_count_rows();
   pl.grid = p.nblk8 < sms ? p.nblk8 : sms;
   const int max_blk = (p.nblk8 + pl.grid - 1) / pl.grid;
   const int max_rg = (max_blk + 1) / 2 + 1;
   size_t off = 512;
-  p.off_tileph = (uint32_t)off;
-  if (p.nph > 1) off += (size_t)(max_rg * 4 + 127) / 128 * 128;
-  p.off_pbuf = (uint32_t)off;
-  off += (size_t)kPartialBufs * kWarps * MT * 512;
   p.off_tile = (uint32_t)off;
   if (p.nph > 1) off += (size_t)max_rg * MT * 512;
+  p.off_pbuf = (uint32_t)off;
+  off += (size_t)kPartialBufs * kConsumers * MT * 512;
+  off = (off + 1023) / 1024 * 1024;   // swizzled tiles repeat every 1024 bytes
   p.off_slots = (uint32_t)off;
   if (off + 2 * (size_t)p.slot_bytes > kSmemLimit) return false;
   const long long stages = (long long)max_rg * p.nph;
@@ -538,8 +617,6 @@ bool fill_plan(const QmmArgs& a, RowsPlan& pl) {
   if (nst < 1) nst = 1;
   p.nst = (int)nst;
   pl.smem = off + (size_t)p.nst * p.slot_bytes;
-  p.row_bytes = a.K * BITS / 8;
-  p.srow_bytes = (long long)groups * 2;
   pl.mt = MT;
   return true;
 }
@@ -550,23 +627,22 @@ RowsPlan make_plan(const QmmArgs& a) {
   if (a.dtype != B200Q_BF16 || !a.transpose || a.w_batched || a.batch != 1) return pl;
   if (a.M < 1 || a.M > 16 || a.N < 1 || a.K < 1) return pl;
   if (a.bits != 2 && a.bits != 4 && a.bits != 8) return pl;
-  if (a.K % (8 * a.group) != 0) return pl;   // scale rows of whole 16-byte pieces
+  if (a.bits == 2 && a.group == 32) return pl;   // a group would be half a 16-byte unit
+  if (a.K % (8 * a.group) != 0) return pl;        // scale rows of whole 16-byte pieces
+  if ((a.K * a.bits / 8) % 128 != 0) return pl;   // packed rows of whole 128-byte chunks
   if (a.N > (1ll << 30)) return pl;
   const int mt = a.M > 8 ? 2 : 1;
   bool ok = false;
 #define B200Q_ROWS_CASE(BITS_, G_)                                                          \
   if (a.bits == BITS_ && a.group == G_)                                                     \
     ok = mt == 2 ? fill_plan<BITS_, G_, 2>(a, pl) : fill_plan<BITS_, G_, 1>(a, pl);
-  B200Q_ROWS_CASE(2, 32) B200Q_ROWS_CASE(2, 64) B200Q_ROWS_CASE(2, 128)
+  B200Q_ROWS_CASE(2, 64) B200Q_ROWS_CASE(2, 128)
   B200Q_ROWS_CASE(4, 32) B200Q_ROWS_CASE(4, 64) B200Q_ROWS_CASE(4, 128)
   B200Q_ROWS_CASE(8, 32) B200Q_ROWS_CASE(8, 64) B200Q_ROWS_CASE(8, 128)
 #undef B200Q_ROWS_CASE
   if (!ok) return pl;
   RowsParams& p = pl.prm;
   p.x = (const __nv_bfloat16*)a.x;
-  p.wq = (const unsigned char*)a.wq;
-  p.scales = (const unsigned char*)a.scales;
-  p.biases = (const unsigned char*)a.biases;
   if (a.peers.n > 0) {
     p.n_out = a.peers.n; p.ld = a.peers.ld; p.col0 = a.peers.col0;
     for (int q = 0; q < a.peers.n; ++q) p.y[q] = (__nv_bfloat16*)a.peers.y[q];
@@ -588,8 +664,46 @@ bool pdl_enabled_rows() {
   return v == 1;
 }
 
+// Stages in flight per SM; B200Q_ROWS_INFLIGHT overrides (tuning).
+int rows_inflight() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_ROWS_INFLIGHT");
+    v = e ? atoi(e) : 3;
+    if (v < 1) v = 1;
+  }
+  return v;
+}
+
 template <int BITS, int G, int MT>
-int launch_rows(const RowsPlan& pl, cudaStream_t st) {
+int launch_rows(const QmmArgs& a, const RowsPlan& pl, cudaStream_t st) {
+  EncodeFn enc = rows_encode_fn();
+  if (!enc) return fail(B200Q_ERR_CUDA, "[quantized_matmul] cuTensorMapEncodeTiled is not available");
+  const RowsParams& p = pl.prm;
+  CUtensorMap map_w, map_s, map_b;
+  {
+    // packed rows as (128 bytes, row, 128-byte chunk of the row)
+    const cuuint64_t row_bytes = (cuuint64_t)a.K * BITS / 8;
+    const cuuint64_t dims[3] = {128, (cuuint64_t)a.N, row_bytes / 128};
+    const cuuint64_t strides[2] = {row_bytes, 128};
+    const cuuint32_t box[3] = {128, 16, (cuuint32_t)p.nch};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint32_t*>(a.wq), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for the packed weights failed (%d)", (int)r);
+  }
+  for (int which = 0; which < 2; ++which) {
+    const cuuint64_t srow = (cuuint64_t)p.groups * 2;
+    const cuuint64_t dims[2] = {srow, (cuuint64_t)a.N};
+    const cuuint64_t strides[1] = {srow};
+    const cuuint32_t box[2] = {128, 16};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(which ? &map_b : &map_s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(which ? a.biases : a.scales),
+                     dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for scales / biases failed (%d)", (int)r);
+  }
   auto kern = qmv_rows_kernel<BITS, G, MT>;
   if (pl.smem > 48 * 1024)
     B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
@@ -603,7 +717,7 @@ int launch_rows(const RowsPlan& pl, cudaStream_t st) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = pdl_enabled_rows() ? 1 : 0;
-  B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, pl.prm));
+  B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map_w, map_s, map_b, pl.prm));
   B200Q_LAUNCH_OK("qmv_rows_kernel");
   return B200Q_OK;
 }
@@ -635,13 +749,14 @@ int qmv_rows(const QmmArgs& a, cudaStream_t st) {
   RowsPlan pl = make_plan(a);
   if (!pl.ok) return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul] qmv_rows: unsupported problem");
   pl.prm.early = weights_constant() ? 1 : 0;
+  pl.prm.inflight = rows_inflight();
   if (a.ws && a.ws_bytes >= kStatusBytes)
     pl.prm.status = reinterpret_cast<uint32_t*>(static_cast<char*>(a.ws) + a.ws_bytes - kStatusBytes);
   int rc = B200Q_ERR_UNSUPPORTED;
 #define B200Q_ROWS_CASE(BITS_, G_)                                                                  \
   if (a.bits == BITS_ && a.group == G_)                                                             \
-    rc = pl.mt == 2 ? launch_rows<BITS_, G_, 2>(pl, st) : launch_rows<BITS_, G_, 1>(pl, st);
-  B200Q_ROWS_CASE(2, 32) B200Q_ROWS_CASE(2, 64) B200Q_ROWS_CASE(2, 128)
+    rc = pl.mt == 2 ? launch_rows<BITS_, G_, 2>(a, pl, st) : launch_rows<BITS_, G_, 1>(a, pl, st);
+  B200Q_ROWS_CASE(2, 64) B200Q_ROWS_CASE(2, 128)
   B200Q_ROWS_CASE(4, 32) B200Q_ROWS_CASE(4, 64) B200Q_ROWS_CASE(4, 128)
   B200Q_ROWS_CASE(8, 32) B200Q_ROWS_CASE(8, 64) B200Q_ROWS_CASE(8, 128)
 #undef B200Q_ROWS_CASE
