@@ -17,13 +17,18 @@
 //    registers for the whole phase, as mma.sync B fragments in the order the unpack produces the
 //    weights: x is read from L2 once per CTA and never touches shared memory.
 //  * Packed words come out of shared memory with ldmatrix (conflict-free on the swizzled tile:
-//    lane (g, t) receives word t of a 16-byte unit of rows g and g+8), are unpacked with
-//    shift + lop3 to the bf16 numbers 128+q ("0x4300 | q") and fed to mma.sync.m16n8k16 as the
-//    A operand.  Scales are applied per group to fp32 group sums; the "128" offset and the biases
-//    come back through two small MMAs against the group sums of x:
-//        y = sum_g s_g * (sum_k x_k (128 + q_k))  +  sum_g (b_g - 128 s_g) * (sum_k x_k).
-//    8-bit fields are treated as two 4-bit fields against (x, 16 x): same unpack, same rate per
-//    byte.  Four independent accumulation chains per warp hide the mma.sync latency.
+//    lane (g, t) receives word t of a 16-byte unit of rows g and g+8) and become mma.sync.m16n8k16
+//    A operands with one AND per register: a bf16 whose high byte is zero is the subnormal number
+//    (low byte) * 2^-133, exactly, and the tensor cores take subnormal inputs exactly, so
+//    "w & 0x000F000F" IS the pair (q_0, q_4) * 2^-133 and "w & 0x00F000F0" the pair (16 q_1, 16 q_5)
+//    * 2^-133; one shift by 8 brings the other two bytes down.  The integer processing pipe that
+//    does the unpacking is what bounds this kernel, and this form needs 5 operations per 8 four-bit
+//    weights (3 per 4 eight-bit weights, 9 per 16 two-bit weights) and no offset correction.
+//    x is pre-multiplied by 2^64 (and 2^60 where the field sits four bits up) when it is put into
+//    registers; the reducer multiplies the sums by 2^69.  (|x| >= 2^64 would overflow; see b200q.h.)
+//    Scales are applied per group to fp32 group sums, the biases come back through one small MMA
+//    against the group sums of x:  y = sum_g s_g * (sum_k x_k q_k) + sum_g b_g * (sum_k x_k).
+//    Four independent accumulation chains per warp hide the mma.sync latency.
 //  * The consumer warps leave fp32 partial tiles in shared memory; the reducer warp adds them in
 //    warp order (the result does not depend on timing), converts and stores y.
 #include <cuda.h>
@@ -58,6 +63,8 @@ constexpr size_t kSmemLimit = 227 * 1024;
 // warp, in a buffer of their own that a test harness reads back with cudaMemcpyFromSymbol.
 #ifdef B200Q_ROWS_PROFILE
 __device__ uint32_t g_rows_prof[160][kConsumers + 4][32];
+__device__ unsigned long long g_rows_t[64][4];   // per launch (mod 64): first CTA start, last CTA start, first end, last end (globaltimer)
+__device__ unsigned int g_rows_launch_in, g_rows_launch_out;
 #define RP_MARK(i)                                                                            \
   do {                                                                                        \
     if (lane == 0 && (i) < 32 && blockIdx.x < 160)                                            \
@@ -67,10 +74,17 @@ __device__ uint32_t g_rows_prof[160][kConsumers + 4][32];
 #define RP_MARK(i)
 #endif
 
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));  // (a & b) | c
-  return d;
+// Non-blocking look at a barrier phase (try_wait may park the thread for a while before it says no).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
 }
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
@@ -120,6 +134,8 @@ __device__ __forceinline__ float sum_bf16x2(uint32_t v) { return bf16lo(v) + bf1
 __host__ __device__ constexpr int cmin(int a, int b) { return a < b ? a : b; }
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
+constexpr int kMaxPhases = 16;
+
 // Compile-time shape of one (bits, group size, token tiles) instantiation.  A "unit" is 16 packed
 // bytes of one row (what one ldmatrix row holds); lane t of a quad owns word t of every unit.
 template <int BITS, int G, int MT>
@@ -128,11 +144,11 @@ struct Cfg {
   static constexpr int GB = G * BITS / 8;                  // packed bytes of one group of one row
   static_assert(GB >= 16, "a group must fill at least one 16-byte unit");
   static constexpr int UG = GB / 16;                       // units per group
-  static constexpr int KW = BITS == 8 ? 4 : (BITS == 4 ? 8 : 16);   // k values per 32-bit word
-  static constexpr int NB = BITS == 2 ? 2 : 1;             // unpack blocks (four bf16 pairs) per word
-  static constexpr int XU = MT * NB * 4;                   // x registers per unit
-  static constexpr int UW = cmax(UG, cmin(64 / XU, 8 * UG));   // units per warp and phase (64 x registers, 8 groups)
-  static constexpr int NGW = UW / UG;                      // groups per warp and phase
+  static constexpr int KW = 32 / BITS;                     // k values per 32-bit word
+  static constexpr int NP = KW / 2;                        // bf16x2 registers a word unpacks to
+  static constexpr int UW = cmax(UG, cmin(cmin(64 / (MT * NP), 8 * UG), 16));   // units per warp and phase
+  static constexpr int NGW = UW / UG;                      // groups per warp and phase (2, 4 or 8)
+  static_assert(NGW >= 2 && NGW <= 8, "groups are processed in pairs, eight at most feed one bias MMA");
 };
 
 struct RowsParams {
@@ -142,9 +158,10 @@ struct RowsParams {
   long long ld, col0;
   int M, N, K;
   int nblk8;            // ceil(N / 8)
-  int groups;           // K / G
-  int nph, gph;         // phases over K, groups per (full) phase
-  int nch, nsb;         // 128-byte chunks of packed bytes / of scales per row and phase
+  int nph;              // phases over K
+  int ph_g0[kMaxPhases];   // first group of the phase
+  int ph_cnt[kMaxPhases];  // groups per warp in the phase (1, 2, 4 or 8; 16 warps)
+  int nch, nsb;         // 128-byte chunks of packed bytes / of scales per row in a TMA box
   int nst;              // ring stages
   uint32_t slot_bytes;  // (nch + 2 * nsb) * 2048
   uint32_t off_slots, off_tile, off_pbuf;
@@ -153,19 +170,37 @@ struct RowsParams {
   int early;            // weights, scales and biases may be read before the previous kernel ended
 };
 
-// Unpacks block `blk` of a packed word into four bf16x2 registers (128+q_i, 128+q_{i+4}).
+// One packed word -> NP registers of two bf16 subnormals each; register i holds fields (i, i + NP)
+// of the word, scaled by 2^-133 and by the power of two in xscale<BITS>(i).
 template <int BITS>
-__device__ __forceinline__ void unpack_block(uint32_t w, int blk, uint32_t (&P)[4]) {
-  constexpr uint32_t kMagic = 0x43004300u;
-  if constexpr (BITS == 4 || BITS == 8) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) P[i] = lop3_and_or(w >> (4 * i), 0x000F000Fu, kMagic);
+__device__ __forceinline__ void unpack_word(uint32_t w, uint32_t* P) {
+  const uint32_t u = w >> 8;
+  if constexpr (BITS == 4) {
+    P[0] = w & 0x000F000Fu; P[1] = w & 0x00F000F0u; P[2] = u & 0x000F000Fu; P[3] = u & 0x00F000F0u;
+  } else if constexpr (BITS == 8) {
+    P[0] = w & 0x00FF00FFu; P[1] = u & 0x00FF00FFu;
   } else {
-    // 16 fields per word; a block is one half word: spread its two bytes to bits 0-7 / 16-23
-    const uint32_t v = __byte_perm(w, 0u, blk ? 0x4342 : 0x4140);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) P[i] = lop3_and_or(v >> (2 * i), 0x00030003u, kMagic);
+    P[0] = w & 0x00030003u; P[1] = w & 0x000C000Cu; P[2] = w & 0x00300030u; P[3] = w & 0x00C000C0u;
+    P[4] = u & 0x00030003u; P[5] = u & 0x000C000Cu; P[6] = u & 0x00300030u; P[7] = u & 0x00C000C0u;
   }
+}
+// bf16x2 constant that x pair i is multiplied with: 2^64 divided by the position weight of field i.
+template <int BITS>
+__device__ __forceinline__ constexpr uint32_t xscale(int i) {
+  // 2^64 = 0x5F80, 2^62 = 0x5E80, 2^60 = 0x5D80, 2^58 = 0x5C80
+  if (BITS == 4) return (i & 1) ? 0x5D805D80u : 0x5F805F80u;
+  if (BITS == 8) return 0x5F805F80u;
+  return (i & 3) == 0 ? 0x5F805F80u : ((i & 3) == 1 ? 0x5E805E80u : ((i & 3) == 2 ? 0x5D805D80u : 0x5C805C80u));
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
 
 template <int BITS, int G, int MT>
@@ -173,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                 const __grid_constant__ CUtensorMap map_b, const RowsParams p) {
   using C = Cfg<BITS, G, MT>;
-  constexpr int NGW = C::NGW, NB = C::NB, UG = C::UG, UW = C::UW, KW = C::KW;
+  constexpr int NGW = C::NGW, NP = C::NP, UG = C::UG, UW = C::UW, KW = C::KW;
   extern __shared__ __align__(1024) unsigned char smem[];
   // header: [0, 128) "stage landed" barriers | [128, 256) "stage consumed" barriers |
   //         [256, 288) "partial buffer free" barriers | 320: abort flag
@@ -191,6 +226,16 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     g_rows_prof[blockIdx.x][warp][31] = (uint32_t)gt;
   }
 #endif
+#ifdef B200Q_ROWS_PROFILE
+  if (tid == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    const unsigned n = atomicAdd(&g_rows_launch_in, 1u);
+    const unsigned id = (n / gridDim.x) & 63;
+    if (n % gridDim.x == 0) g_rows_t[id][0] = gt;
+    atomicMax(&g_rows_t[id][1], gt);
+  }
+#endif
   asm volatile("griddepcontrol.launch_dependents;");
   if (tid == kConsumers * 32) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -206,54 +251,81 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   const int row_end = min(b1 * 8, p.N);
   const int nst = p.nst;
 
-  if (tid == 0) {
-    for (int i = 0; i < nst; ++i) {
-      mbar_init(full0 + 8 * i, 1);
-      mbar_init(done0 + 8 * i, kConsumers);
-    }
-    for (int i = 0; i < kPartialBufs; ++i) mbar_init(pfree0 + 8 * i, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-  RP_MARK(1);
-
+  // Barriers are set up by the loader thread, which then starts requesting weights at once; the
+  // other warps meet it at a named barrier (id 1) only when they first need the barriers - the
+  // consumers after their x values are in registers.
   if (warp >= kConsumers) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
     if (warp == kConsumers) {
+      if (lane == 0) {
+        for (int i = 0; i < nst; ++i) {
+          mbar_init(full0 + 8 * i, 1);
+          mbar_init(done0 + 8 * i, kConsumers);
+        }
+        for (int i = 0; i < kPartialBufs; ++i) mbar_init(pfree0 + 8 * i, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      }
+      __syncwarp();
+      asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+      RP_MARK(1);
       // ================================= loader warp ==========================================
       // Without the caller's promise the weights may have been written by the previous kernel.
       if (!p.early) asm volatile("griddepcontrol.wait;" ::: "memory");
       RP_MARK(2);
       if (lane == 0) {
-        const uint32_t stage_bytes = p.slot_bytes;
-        const int chunks_per_phase = p.gph * C::GB / 128;
+        // This one thread shares its scheduler with four busy consumer warps: everything it needs
+        // per stage is kept incremental (no divisions, no parameter reloads).
+        const uint32_t stage_bytes = p.slot_bytes, sb_off = (uint32_t)p.nch * 2048, bb_off = (uint32_t)(p.nch + p.nsb) * 2048;
+#ifdef B200Q_ROWS_PROFILE
+        const int dbg = p.inflight >> 8;
+        const int nsb = (dbg & 1) ? 0 : p.nsb, inflight = p.inflight & 255;
+        const uint32_t stage_bytes_dbg = (dbg & 1) ? (uint32_t)p.nch * 2048 : stage_bytes;
+#define STAGE_TX stage_bytes_dbg
+#else
+        const int nsb = p.nsb, inflight = p.inflight;
+#define STAGE_TX stage_bytes
+#endif
+        int slot = 0, use = 0;        // ring position of stage s
+        int lslot = 0, luse = 0;      // ring position of the oldest stage not yet known to have landed
         int landed = 0, iph = 0, irg = 0;
+        int grp0 = p.ph_g0[0];
+        uint32_t dst = smem_base + p.off_slots;
         for (int s = 0; s < total; ++s) {
-          const int slot = s % nst;
           // slot free: all consumer warps arrived for the stage that used it last
-          if (s >= nst && !mbar_wait(done0 + 8 * slot, ((s - nst) / nst) & 1, abort_flag)) break;
-          // at most p.inflight stages outstanding
-          while (landed < s && tc::mbar_try(full0 + 8 * (landed % nst), (landed / nst) & 1)) ++landed;
-          if (s - landed >= p.inflight) {
-            const int w = s - p.inflight;
-            if (!mbar_wait(full0 + 8 * (w % nst), (w / nst) & 1, abort_flag)) break;
-            landed = w + 1;
+          if (use > 0 && !mbar_wait(done0 + 8 * slot, (use - 1) & 1, abort_flag)) break;
+          // at most `inflight` stages outstanding
+          while (landed < s && mbar_test(full0 + 8 * lslot, luse & 1)) {
+            ++landed;
+            if (++lslot == nst) { lslot = 0; ++luse; }
           }
+          while (s - landed >= inflight) {
+            if (!mbar_wait(full0 + 8 * lslot, luse & 1, abort_flag)) break;
+            ++landed;
+            if (++lslot == nst) { lslot = 0; ++luse; }
+          }
+          if (*abort_flag) break;
           const int row0 = (b0 + 2 * irg) * 8;
           const uint32_t bar = full0 + 8 * slot;
-          const uint32_t dst = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
+#ifdef B200Q_ROWS_PROFILE
+          if (5 + 3 * s < 30 && blockIdx.x < 160) g_rows_prof[blockIdx.x][warp][5 + 3 * s] = (uint32_t)(clock64() - rp_entry);
+#endif
           // rows past N and chunks past K are zero-filled by the copy engine and still counted
-          mbar_expect_tx(bar, stage_bytes);
-          tma_load_3d(dst, &map_w, 0, row0, iph * chunks_per_phase, bar);
-          for (int i = 0; i < p.nsb; ++i) {
-            tc::tma_load_2d(dst + (p.nch + i) * 2048, &map_s, iph * p.gph * 2 + 128 * i, row0, bar);
-            tc::tma_load_2d(dst + (p.nch + p.nsb + i) * 2048, &map_b, iph * p.gph * 2 + 128 * i, row0, bar);
+          mbar_expect_tx(bar, STAGE_TX);
+          tma_load_3d(dst, &map_w, 0, row0, grp0 * (C::GB / 16) / 8, bar);
+#ifdef B200Q_ROWS_PROFILE
+          if (6 + 3 * s < 30 && blockIdx.x < 160) g_rows_prof[blockIdx.x][warp][6 + 3 * s] = (uint32_t)(clock64() - rp_entry);
+#endif
+          for (int i = 0; i < nsb; ++i) {
+            tc::tma_load_2d(dst + sb_off + i * 2048, &map_s, grp0 * 2 + 128 * i, row0, bar);
+            tc::tma_load_2d(dst + bb_off + i * 2048, &map_b, grp0 * 2 + 128 * i, row0, bar);
           }
 #ifdef B200Q_ROWS_PROFILE
-          if (5 + s < 30 && blockIdx.x < 160) g_rows_prof[blockIdx.x][warp][5 + s] = (uint32_t)(clock64() - rp_entry);
+          if (7 + 3 * s < 30 && blockIdx.x < 160) g_rows_prof[blockIdx.x][warp][7 + 3 * s] = (uint32_t)(clock64() - rp_entry);
 #endif
-          if (++irg == nrg) { irg = 0; ++iph; }
+          dst += stage_bytes;
+          if (++slot == nst) { slot = 0; ++use; dst = smem_base + p.off_slots; }
+          if (++irg == nrg) { irg = 0; ++iph; grp0 = p.ph_g0[iph < p.nph ? iph : 0]; }
         }
       }
       RP_MARK(30);
@@ -261,31 +333,27 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // ================================= reducer warp =========================================
       // Adds the consumer warps' partial tiles of a finished stage in warp order, frees the
       // partial buffer, and stores y (or keeps running sums while K is walked in phases).
+      asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
       asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be in use by the previous kernel
-      int rph = 0, rrg = 0;
+      int rph = 0, rrg = 0, rslot = 0, ruse = 0;
       for (int red = 0; red < total; ++red) {
-        if (!mbar_wait(done0 + 8 * (red % nst), (red / nst) & 1, abort_flag)) break;
+        if (!mbar_wait(done0 + 8 * rslot, ruse & 1, abort_flag)) break;
+        if (++rslot == nst) { rslot = 0; ++ruse; }
         RP_MARK(5 + 2 * red);
-        const int gp = min(p.gph, p.groups - rph * p.gph);
-        const int nact = gp < kConsumers ? gp : kConsumers;
         const int pbi = red % kPartialBufs;
         const float4* pb = reinterpret_cast<const float4*>(smem + p.off_pbuf + (size_t)pbi * (kConsumers * MT * 512)) + lane;
         float sum[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          int w = 0;
-          for (; w + 4 <= nact; w += 4) {   // four independent loads, then the additions in warp order
+#pragma unroll
+          for (int w = 0; w < kConsumers; w += 4) {   // four independent loads, then the additions in warp order
             const float4 v0 = pb[((w + 0) * MT + mt) * 32], v1 = pb[((w + 1) * MT + mt) * 32];
             const float4 v2 = pb[((w + 2) * MT + mt) * 32], v3 = pb[((w + 3) * MT + mt) * 32];
             acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
             acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
             acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
             acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
-          }
-          for (; w < nact; ++w) {
-            const float4 v = pb[(w * MT + mt) * 32];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
           }
           sum[mt][0] = acc.x; sum[mt][1] = acc.y; sum[mt][2] = acc.z; sum[mt][3] = acc.w;
         }
@@ -313,7 +381,8 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
               const int row = row0 + g + (c >> 1) * 8;
               const int tok = mt * 8 + 2 * t + (c & 1);
               if (row < row_end && tok < p.M) {
-                const __nv_bfloat16 o = __float2bfloat16_rn(sum[mt][c]);
+                // undo the 2^-133 of the subnormal weights and the 2^64 of x
+                const __nv_bfloat16 o = __float2bfloat16_rn(sum[mt][c] * 0x1p69f);
                 const long long at = (long long)tok * p.ld + p.col0 + row;
                 p.y[0][at] = o;
                 for (int q = 1; q < p.n_out; ++q) p.y[q][at] = o;
@@ -325,8 +394,20 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         RP_MARK(6 + 2 * red);
       }
       RP_MARK(30);
+#ifdef B200Q_ROWS_PROFILE
+      if (lane == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        const unsigned n = atomicAdd(&g_rows_launch_out, 1u);
+        const unsigned id = (n / gridDim.x) & 63;
+        if (n % gridDim.x == 0) g_rows_t[id][2] = gt;
+        atomicMax(&g_rows_t[id][3], gt);
+      }
+#endif
+    } else {
+      asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");   // idle companions of the service warps
     }
-    if (*abort_flag && lane == 0 && warp == kConsumers && p.status) atomicMax(&p.status[0], 7u);
+    if (warp == kConsumers && lane == 0 && *abort_flag && p.status) atomicMax(&p.status[0], 7u);
     return;
   }
 
@@ -334,23 +415,34 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsConsumer));
   asm volatile("griddepcontrol.wait;" ::: "memory");
   RP_MARK(2);
-  uint32_t X[UW][NB][MT][4];      // B fragments of this warp's K slice
-  uint32_t sx_hi[MT], sx_lo[MT];  // group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)
-  int cnt = 0, g0 = 0;
+  uint32_t X[UW][MT][NP];         // B fragments of this warp's K slice, pre-scaled
+  uint32_t sx_hi[MT], sx_lo[MT];  // 2^-69 * group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)
+  uint32_t woff[UW / 2];          // this lane's ldmatrix addresses inside a stage
+  uint32_t soff = 0;              // scale of (row g, first group of the slice) inside a stage
+  int cnt = 0;
   int ph = 0, rg = 0, slot = 0, use = 0, pbi = 0, pbe = 0;
+  // ldmatrix roles of this lane: matrix m = lane / 8 covers rows (m & 1) * 8 .. +7 of unit (m >> 1)
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_unit = lane >> 4, lm_x = lane & 7;
 
   auto setup_phase = [&]() {
-    const int gp = min(p.gph, p.groups - ph * p.gph);
-    const int base = gp / kConsumers, rem = gp - base * kConsumers;
-    cnt = base + (warp < rem ? 1 : 0);
-    g0 = warp * base + min(warp, rem);
+    cnt = p.ph_cnt[ph];
+    const int g0 = warp * cnt;       // first group of this warp inside the phase
+    const int u0 = g0 * UG;
+#pragma unroll
+    for (int j = 0; j < UW / 2; ++j) {
+      const int U = u0 + 2 * j + lm_unit;
+      woff[j] = (uint32_t)(U >> 3) * 2048 + lm_row * 128 + (((U & 7) ^ lm_x) << 4);
+    }
+    // scales: 128-byte rows, 16-byte units xor-ed with the row number mod 8; a warp's (at most 8)
+    // groups lie inside one unit; the same entry of row g + 8 is 1024 bytes further on
+    soff = (uint32_t)(p.nch + ((2 * g0) >> 7)) * 2048 + g * 128 + (((((2 * g0) >> 4) & 7) ^ g) << 4) + ((2 * g0) & 15);
     float sx[NGW][MT];
 #pragma unroll
     for (int j = 0; j < NGW; ++j)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) sx[j][mt] = 0.0f;
     // unit i of the slice: 4 * KW consecutive k, of which this lane owns KW starting at t * KW
-    const long long k0 = (long long)(ph * p.gph + g0) * G + t * KW;
+    const long long k0 = (long long)(p.ph_g0[ph] + g0) * G + t * KW;
 #pragma unroll
     for (int i = 0; i < UW; ++i) {
 #pragma unroll
@@ -358,26 +450,30 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int tok = mt * 8 + g;
         const bool live = i < cnt * UG && tok < p.M;
         const __nv_bfloat16* xp = p.x + (long long)tok * p.K + k0 + i * (4 * KW);
+        uint32_t r[NP];   // pair i = (x_i, x_{i + NP})
         if constexpr (BITS == 8) {
-          // one word = 4 k; pairs (x0,x2), 16(x0,x2), (x1,x3), 16(x1,x3)
           uint2 v = make_uint2(0, 0);
           if (live) v = ldg_nc_u64(xp);
           sx[i / UG][mt] += sum_bf16x2(v.x) + sum_bf16x2(v.y);
-          const uint32_t a = __byte_perm(v.x, v.y, 0x5410), b = __byte_perm(v.x, v.y, 0x7632);
-          X[i][0][mt][0] = a; X[i][0][mt][1] = mul_bf16x2(a, 0x41804180u);
-          X[i][0][mt][2] = b; X[i][0][mt][3] = mul_bf16x2(b, 0x41804180u);
+          r[0] = __byte_perm(v.x, v.y, 0x5410); r[1] = __byte_perm(v.x, v.y, 0x7632);
+        } else if constexpr (BITS == 4) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (live) v = ldg_nc_u128(xp);
+          sx[i / UG][mt] += (sum_bf16x2(v.x) + sum_bf16x2(v.y)) + (sum_bf16x2(v.z) + sum_bf16x2(v.w));
+          r[0] = __byte_perm(v.x, v.z, 0x5410); r[1] = __byte_perm(v.x, v.z, 0x7632);
+          r[2] = __byte_perm(v.y, v.w, 0x5410); r[3] = __byte_perm(v.y, v.w, 0x7632);
         } else {
-#pragma unroll
-          for (int nb = 0; nb < NB; ++nb) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (live) v = ldg_nc_u128(xp + 8 * nb);
-            sx[i / UG][mt] += (sum_bf16x2(v.x) + sum_bf16x2(v.y)) + (sum_bf16x2(v.z) + sum_bf16x2(v.w));
-            X[i][nb][mt][0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
-            X[i][nb][mt][1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
-            X[i][nb][mt][2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
-            X[i][nb][mt][3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
-          }
+          uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+          if (live) { a = ldg_nc_u128(xp); b = ldg_nc_u128(xp + 8); }
+          sx[i / UG][mt] += (sum_bf16x2(a.x) + sum_bf16x2(a.y)) + (sum_bf16x2(a.z) + sum_bf16x2(a.w)) +
+                            (sum_bf16x2(b.x) + sum_bf16x2(b.y)) + (sum_bf16x2(b.z) + sum_bf16x2(b.w));
+          r[0] = __byte_perm(a.x, b.x, 0x5410); r[1] = __byte_perm(a.x, b.x, 0x7632);
+          r[2] = __byte_perm(a.y, b.y, 0x5410); r[3] = __byte_perm(a.y, b.y, 0x7632);
+          r[4] = __byte_perm(a.z, b.z, 0x5410); r[5] = __byte_perm(a.z, b.z, 0x7632);
+          r[6] = __byte_perm(a.w, b.w, 0x5410); r[7] = __byte_perm(a.w, b.w, 0x7632);
         }
+#pragma unroll
+        for (int q = 0; q < NP; ++q) X[i][mt][q] = mul_bf16x2(r[q], xscale<BITS>(q));
       }
     }
     // group sums over the quad, then lane t keeps groups 2t and 2t+1 (the k slots it feeds)
@@ -393,12 +489,14 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           if (j & 1) e1 = v; else e0 = v;
         }
       }
+      e0 *= 0x1p-69f; e1 *= 0x1p-69f;   // the scale every other term of the sums carries
       const uint32_t hi = pack_bf16x2(e0, e1);
       sx_hi[mt] = hi;
       sx_lo[mt] = pack_bf16x2(e0 - bf16lo(hi), e1 - bf16hi(hi));
     }
   };
   setup_phase();
+  asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");   // the barriers exist from here on
   {
     // The first mma.sync of a kernel is slow (the tensor pipe wakes up): issue one now, while the
     // first stage is in flight anyway.  Its result is never used.
@@ -408,134 +506,106 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   }
   RP_MARK(4);
 
-  // ldmatrix roles of this lane: matrix m = lane / 8 covers rows (m & 1) * 8 .. +7 of unit (m >> 1)
-  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_unit = lane >> 4, lm_x = lane & 7;
+  const uint32_t pb_mine = smem_base + p.off_pbuf + (uint32_t)(warp * MT * 32 + lane) * 16;
+  uint32_t sb = smem_base + p.off_slots;   // stage the warp works on
   for (int s = 0; s < total; ++s) {
     if (!mbar_wait(full0 + 8 * slot, use & 1, abort_flag)) break;
     RP_MARK(5 + 3 * s);
-    if (cnt > 0) {
-      const uint32_t sb = smem_base + p.off_slots + (uint32_t)slot * p.slot_bytes;
-      const unsigned char* sbp = smem + p.off_slots + (size_t)slot * p.slot_bytes;
-      // scale / bias of (row g, group J of the phase): 128-byte rows, 16-byte units xor-ed with the
-      // row number mod 8; the same entry of row g + 8 is 1024 bytes (512 elements) further on
-      auto sc_ptr = [&](int tile0, int J) -> const unsigned short* {
-        const int b = 2 * J;
-        return reinterpret_cast<const unsigned short*>(sbp + (size_t)(tile0 + (b >> 7)) * 2048 + g * 128 +
-                                                        ((((b >> 4) & 7) ^ g) << 4) + (b & 15));
-      };
-      float out[MT][4];
+    float out[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) out[mt][c] = 0.0f;
+#ifdef B200Q_ROWS_PROFILE
+    if (!((p.inflight >> 8) & 2))
+#endif
+    {
+    // mma.sync results come back after many cycles: keep four independent accumulation chains going
+    // per warp (two groups at a time, each group's k steps dealt round-robin to SPLIT accumulators,
+    // MT token tiles).  A group past the warp's share (cnt < NGW) would multiply a neighbour's
+    // bytes with x registers that are zero: it is skipped, pairs are whole because cnt is even or 1.
+    constexpr int STEPS = UG * NP / 2;   // mma k steps per group
+    constexpr int SPLIT = cmax(1, cmin(4 / (MT * 2), STEPS));
+    const uint32_t sa = sb + soff;
+#pragma unroll
+    for (int gq = 0; gq < NGW; gq += 2) {
+      if (gq < cnt) {
+        // packed words: lane (g, t) gets word t of unit i for rows g (wl) and g + 8 (wh)
+        uint32_t wl[2 * UG], wh[2 * UG];
+#pragma unroll
+        for (int i = 0; i < 2 * UG; i += 2) ldmatrix_x4(sb + woff[(gq * UG + i) / 2], wl[i], wh[i], wl[i + 1], wh[i + 1]);
+        float acc[2][MT][SPLIT][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int q = 0; q < SPLIT; ++q)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[u][mt][q][c] = 0.0f;
+#pragma unroll
+        for (int iu = 0; iu < UG; ++iu) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            uint32_t Pl[NP], Ph[NP];
+            unpack_word<BITS>(wl[u * UG + iu], Pl);
+            unpack_word<BITS>(wh[u * UG + iu], Ph);
+#pragma unroll
+            for (int st = 0; st < NP / 2; ++st)
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+                mma_bf16(acc[u][mt][(iu * (NP / 2) + st) % SPLIT], Pl[2 * st], Ph[2 * st], Pl[2 * st + 1], Ph[2 * st + 1],
+                         X[(gq + u) * UG + iu][mt][2 * st], X[(gq + u) * UG + iu][mt][2 * st + 1]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          // a group beyond cnt (cnt == 1) contributes acc == 0 times a finite neighbour's scale
+          const float s_l = __uint_as_float(lds_u16(sa + 2 * (gq + u)) << 16);
+          const float s_h = __uint_as_float(lds_u16(sa + 1024 + 2 * (gq + u)) << 16);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int q = 1; q < SPLIT; ++q)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[u][mt][0][c] += acc[u][mt][q][c];
+            out[mt][0] = fmaf(s_l, acc[u][mt][0][0], out[mt][0]);
+            out[mt][1] = fmaf(s_l, acc[u][mt][0][1], out[mt][1]);
+            out[mt][2] = fmaf(s_h, acc[u][mt][0][2], out[mt][2]);
+            out[mt][3] = fmaf(s_h, acc[u][mt][0][3], out[mt][3]);
+          }
+        }
+      }
+    }
+    // biases: b_g * sum_k x_k through one MMA, k slots 2t, 2t+1 (hi part of the sum) / +8 (lo part)
+    {
+      uint32_t bl = 0, bh = 0;
+      const uint32_t ba = sa + (uint32_t)p.nsb * 2048;
+      if (cnt >= 2) {
+        if (2 * t < cnt) { bl = lds_u32(ba + 4 * t); bh = lds_u32(ba + 1024 + 4 * t); }
+      } else if (t == 0) {
+        bl = lds_u16(ba); bh = lds_u16(ba + 1024);
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mma_bf16(out[mt], bl, bh, bl, bh, sx_hi[mt], sx_lo[mt]);
+    }
+    }
+    RP_MARK(6 + 3 * s);
+    // the partial buffer of this stage was read by the reducer kPartialBufs stages ago
+    if (pbe > 0 && !mbar_wait(pfree0 + 8 * pbi, (pbe - 1) & 1, abort_flag)) break;
+    {
+      const uint32_t pa = pb_mine + (uint32_t)pbi * (kConsumers * MT * 512);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) out[mt][c] = 0.0f;
-      // mma.sync results come back after ~100 cycles: keep four independent accumulation chains
-      // going per warp (PAIR groups at a time, each group's k steps dealt round-robin to SPLIT
-      // accumulators, MT token tiles).
-      constexpr int PAIR = NGW >= 2 ? 2 : 1;
-      constexpr int STEPS = UG * NB * 2;   // mma k steps per group
-      constexpr int SPLIT = cmax(1, cmin(4 / (MT * PAIR), STEPS));
-      constexpr int PU = PAIR * UG;        // units per iteration (even)
-      static_assert(PU % 2 == 0, "units are fetched two at a time");
-      const int u0 = g0 * UG;              // first unit of this warp in the stage
-#pragma unroll
-      for (int gq = 0; gq < NGW; gq += PAIR) {
-        if (gq < cnt) {
-          // packed words: lane (g, t) gets word t of unit i for rows g (wl) and g + 8 (wh)
-          uint32_t wl[PU], wh[PU];
-#pragma unroll
-          for (int i = 0; i < PU; i += 2) {
-            const int U = u0 + gq * UG + i + lm_unit;
-            const uint32_t addr = sb + (uint32_t)(U >> 3) * 2048 + lm_row * 128 + (((U & 7) ^ lm_x) << 4);
-            ldmatrix_x4(addr, wl[i], wh[i], wl[i + 1], wh[i + 1]);
-          }
-          float s_l[PAIR], s_h[PAIR];
-#pragma unroll
-          for (int u = 0; u < PAIR; ++u) {
-            // a group past the warp's share multiplies a neighbour's packed bytes (finite after the
-            // unpack) with x registers that are zero; its scale is forced to zero
-            const bool live = gq + u < cnt;
-            const unsigned short* sp = sc_ptr(p.nch, g0 + gq + u);
-            s_l[u] = live ? __uint_as_float((uint32_t)sp[0] << 16) : 0.0f;
-            s_h[u] = live ? __uint_as_float((uint32_t)sp[512] << 16) : 0.0f;
-          }
-          float acc[PAIR][MT][SPLIT][4];
-#pragma unroll
-          for (int u = 0; u < PAIR; ++u)
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-              for (int q = 0; q < SPLIT; ++q)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[u][mt][q][c] = 0.0f;
-#pragma unroll
-          for (int iu = 0; iu < UG; ++iu) {
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-              uint32_t Pl[PAIR][4], Ph[PAIR][4];
-#pragma unroll
-              for (int u = 0; u < PAIR; ++u) {
-                unpack_block<BITS>(wl[u * UG + iu], nb, Pl[u]);
-                unpack_block<BITS>(wh[u * UG + iu], nb, Ph[u]);
-              }
-#pragma unroll
-              for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int u = 0; u < PAIR; ++u)
-#pragma unroll
-                  for (int mt = 0; mt < MT; ++mt)
-                    mma_bf16(acc[u][mt][((iu * NB + nb) * 2 + h) % SPLIT], Pl[u][2 * h], Ph[u][2 * h], Pl[u][2 * h + 1],
-                             Ph[u][2 * h + 1], X[(gq + u) * UG + iu][nb][mt][2 * h], X[(gq + u) * UG + iu][nb][mt][2 * h + 1]);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < PAIR; ++u)
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-              for (int q = 1; q < SPLIT; ++q)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[u][mt][0][c] += acc[u][mt][q][c];
-              out[mt][0] = fmaf(s_l[u], acc[u][mt][0][0], out[mt][0]);
-              out[mt][1] = fmaf(s_l[u], acc[u][mt][0][1], out[mt][1]);
-              out[mt][2] = fmaf(s_h[u], acc[u][mt][0][2], out[mt][2]);
-              out[mt][3] = fmaf(s_h[u], acc[u][mt][0][3], out[mt][3]);
-            }
-        }
-      }
-      // biases and the unpack offset: (b_g - OFFSET * s_g) * sum_k x_k, k slots 2t, 2t+1 (hi) / +8 (lo)
-      {
-        uint32_t bl = 0, bh = 0, sl = 0, sh = 0;
-        if (2 * t < cnt) {
-          const bool two = 2 * t + 1 < cnt;
-          const unsigned short* ps0 = sc_ptr(p.nch, g0 + 2 * t);
-          const unsigned short* pb0 = sc_ptr(p.nch + p.nsb, g0 + 2 * t);
-          const unsigned short* ps1 = sc_ptr(p.nch, g0 + 2 * t + (two ? 1 : 0));
-          const unsigned short* pb1 = sc_ptr(p.nch + p.nsb, g0 + 2 * t + (two ? 1 : 0));
-          sl = ps0[0] | (two ? (uint32_t)ps1[0] << 16 : 0u);
-          sh = ps0[512] | (two ? (uint32_t)ps1[512] << 16 : 0u);
-          bl = pb0[0] | (two ? (uint32_t)pb1[0] << 16 : 0u);
-          bh = pb0[512] | (two ? (uint32_t)pb1[512] << 16 : 0u);
-        }
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          mma_bf16(out[mt], bl, bh, bl, bh, sx_hi[mt], sx_lo[mt]);
-          mma_bf16(out[mt], sl, sh, sl, sh, mul_bf16x2(sx_hi[mt], 0xC300C300u), mul_bf16x2(sx_lo[mt], 0xC300C300u));
-          if constexpr (BITS == 8)
-            mma_bf16(out[mt], sl, sh, sl, sh, mul_bf16x2(sx_hi[mt], 0xC500C500u), mul_bf16x2(sx_lo[mt], 0xC500C500u));
-        }
-      }
-      RP_MARK(6 + 3 * s);
-      // the partial buffer of this stage was read by the reducer kPartialBufs stages ago
-      if (pbe > 0 && !mbar_wait(pfree0 + 8 * pbi, (pbe - 1) & 1, abort_flag)) break;
-      float4* pb = reinterpret_cast<float4*>(smem + p.off_pbuf + (size_t)pbi * (kConsumers * MT * 512)) + (warp * MT) * 32 + lane;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) pb[mt * 32] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(pa + mt * 512), "f"(out[mt][0]), "f"(out[mt][1]),
+                     "f"(out[mt][2]), "f"(out[mt][3]) : "memory");
     }
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(done0 + 8 * slot);   // release: the partial tile is visible to the reducer
     RP_MARK(7 + 3 * s);
     // advance to the next stage
-    if (++slot == nst) { slot = 0; ++use; }
+    sb += p.slot_bytes;
+    if (++slot == nst) { slot = 0; ++use; sb = smem_base + p.off_slots; }
     if (++pbi == kPartialBufs) { pbi = 0; ++pbe; }
     if (++rg == nrg) {
       rg = 0;
@@ -588,13 +658,21 @@ bool fill_plan(const QmmArgs& a, RowsPlan& pl) {
   using C = Cfg<BITS, G, MT>;
   RowsParams& p = pl.prm;
   const int groups = (int)(a.K / G);
-  const int cap = kConsumers * C::NGW;
-  p.nph = (groups + cap - 1) / cap;
-  p.gph = ((groups + p.nph - 1) / p.nph + 7) / 8 * 8;   // whole 16-byte pieces of scales, whole 128-byte chunks of W
-  if (p.gph > cap) return false;
-  p.groups = groups;
-  p.nch = (p.gph * C::GB + 127) / 128;
-  p.nsb = (p.gph * 2 + 127) / 128;
+  if (groups % kConsumers != 0) return false;   // every phase gives all 16 warps the same number of groups
+  // phases of 16 * c groups, c a power of two: first as many full ones as fit, then the remainder
+  p.nph = 0;
+  for (int g0 = 0, rem = groups; rem > 0;) {
+    int c = C::NGW;
+    while (kConsumers * c > rem) c >>= 1;
+    if (p.nph == kMaxPhases) return false;
+    p.ph_g0[p.nph] = g0;
+    p.ph_cnt[p.nph] = c;
+    ++p.nph;
+    g0 += kConsumers * c;
+    rem -= kConsumers * c;
+  }
+  p.nch = kConsumers * C::NGW * C::GB / 128;          // box of a full phase
+  p.nsb = (kConsumers * C::NGW * 2 + 127) / 128;
   if (p.nch > 256) return false;
   p.slot_bytes = (uint32_t)(p.nch + 2 * p.nsb) * 2048;
   p.nblk8 = (int)((a.N + 7) / 8);
@@ -628,8 +706,7 @@ RowsPlan make_plan(const QmmArgs& a) {
   if (a.M < 1 || a.M > 16 || a.N < 1 || a.K < 1) return pl;
   if (a.bits != 2 && a.bits != 4 && a.bits != 8) return pl;
   if (a.bits == 2 && a.group == 32) return pl;   // a group would be half a 16-byte unit
-  if (a.K % (8 * a.group) != 0) return pl;        // scale rows of whole 16-byte pieces
-  if ((a.K * a.bits / 8) % 128 != 0) return pl;   // packed rows of whole 128-byte chunks
+  if (a.K % (16 * a.group) != 0) return pl;       // 16 warps, whole groups each (implies 128-byte row chunks)
   if (a.N > (1ll << 30)) return pl;
   const int mt = a.M > 8 ? 2 : 1;
   bool ok = false;
@@ -670,7 +747,7 @@ int rows_inflight() {
   if (v < 0) {
     const char* e = getenv("B200Q_ROWS_INFLIGHT");
     v = e ? atoi(e) : 3;
-    if (v < 1) v = 1;
+    if ((v & 255) < 1) v = 1;
   }
   return v;
 }
@@ -694,7 +771,7 @@ int launch_rows(const QmmArgs& a, const RowsPlan& pl, cudaStream_t st) {
     if (r != CUDA_SUCCESS) return fail(B200Q_ERR_CUDA, "[quantized_matmul] tensor map for the packed weights failed (%d)", (int)r);
   }
   for (int which = 0; which < 2; ++which) {
-    const cuuint64_t srow = (cuuint64_t)p.groups * 2;
+    const cuuint64_t srow = (cuuint64_t)(a.K / G) * 2;
     const cuuint64_t dims[2] = {srow, (cuuint64_t)a.N};
     const cuuint64_t strides[1] = {srow};
     const cuuint32_t box[2] = {128, 16};
