@@ -261,6 +261,35 @@ int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local, const void
                              void* stream);
 int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_local, void* stream);
 int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream);
+/*
+ * The same two operators with b200q_peer_signal folded into the matmul: the last thread block
+ * to finish its peer stores fences at system scope, adds n_peers to the local epoch and 1 to
+ * every rank's flag, so a step is two launches (matmul, wait) instead of three.
+ * counter_local is one more device word of this rank (starts at zero, left at zero) that counts
+ * finished thread blocks.  Where the selected kernel has no such epilogue (the register-path
+ * decode kernel for 3-, 5- and 6-bit weights) the signal is launched separately, as before.
+ * The exchange these replace: AllGather::eval_gpu (mlx/backend/cuda/distributed.cu:57-83).
+ */
+int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                             void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
+                             int64_t M, int64_t N_local, int64_t K, int group_size, int bits,
+                             uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
+                             void* ws, size_t ws_bytes, void* stream);
+int b200q_gather_qmm_sharded_signal(const void* x, const uint32_t* wq_local, const void* scales_local,
+                                    const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
+                                    int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
+                                    int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                                    int64_t N, int64_t K, int group_size, int bits,
+                                    uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
+                                    void* ws, size_t ws_bytes, void* stream);
+/*
+ * Bound of b200q_peer_wait in milliseconds (process-wide, default about 1000; <= 0 restores the
+ * default).  When the bound runs out the wait stores code 6 in status[0] and the stream goes on
+ * with an incomplete buffer: the caller must read the status (b200q_read_status) before it uses
+ * a result whose peers may lag by more than the bound.  No counterpart in the reference, whose
+ * NCCL calls block without a bound (mlx/distributed/nccl/nccl.cpp:346-358).
+ */
+void b200q_set_peer_wait_limit_ms(int ms);
 
 /*
  * K-sharded linear with the all_reduce fused into the exchange (QuantizedShardedToAllLinear of
@@ -300,7 +329,7 @@ int b200q_gguf_repack(const void* blocks, int gguf_type, int64_t n_blocks, uint3
 
 /*
  * Introspection for tests and benchmarks: name of the kernel family b200q_qmm would
- * launch for this problem ("qmv_rows", "qmv_mma", "qmv_stream", "qmv_bulk", "qmv_tc", "qmm_tcgen05",
+ * launch for this problem ("qmv_rows", "qmv_mma", "qmm_tcgen05", "qvm",
  * "qmm_generic").
  */
 const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K,

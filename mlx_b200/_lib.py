@@ -44,6 +44,11 @@ SIGNATURES = {
     "b200q_qmm_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i64, _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_gather_qmm_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
                                       _i64, _i64, _i, _i, _vp, _sz, _vp]),
+    "b200q_qmm_sharded_signal": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i64, _i64, _i64, _i, _i, _vp, _vp, _vp,
+                                      _vp, _sz, _vp]),
+    "b200q_gather_qmm_sharded_signal": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i64, _i64, _i64, _i64,
+                                             _i64, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200q_set_peer_wait_limit_ms": (None, [_i]),
     "b200q_peer_signal": (_i, [_vp, _i, _vp, _vp]),
     "b200q_peer_wait": (_i, [_vp, _vp, _vp, _vp]),
     "b200q_peer_reduce": (_i, [_vp, _i, _i64, _i64, _vp, _i, _vp]),

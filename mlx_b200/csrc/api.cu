@@ -2,10 +2,11 @@
 //
 // Kernel selection for b200q_qmm (the role of QuantizedMatmul::eval_gpu's dispatch,
 // mlx/backend/cuda/quantized/quantized.cpp:106-136):
-//   bf16, transpose, M <= 16, K % 128 == 0            -> qmv_mma     (HBM-bound decode)
-//   (B200Q_QMV_IMPL=bulk: 4-bit, K % 512 == 0         -> qmv_bulk, the bulk-copy staged variant)
-//   bf16, transpose, M  > 16, K % 128 == 0, N % 8 == 0 -> qmm_tcgen05 (TMA + tcgen05 + TMEM)
-//   everything else                                   -> qmm_generic
+//   bf16, transpose, M <= 16, bits 2/4/8, K % (16 * group) == 0 -> qmv_rows    (HBM-bound decode)
+//   bf16, transpose, M <= 16, K % 128 == 0 (any width)           -> qmv_mma     (register-path decode)
+//   bf16, transpose, M  > 16, K % 128 == 0, N % 8 == 0           -> qmm_tcgen05 (TMA + tcgen05 + TMEM)
+//   transpose == 0, M <= 4, bits 2/4/8                           -> qvm
+//   everything else                                              -> qmm_generic
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -32,7 +33,7 @@ void count_launch(int n) { g_launches += (uint64_t)n; }
 
 namespace {
 
-enum class Path { QmvRows, QmvStream, QmvTc, QmvBulk, Qmv, Tc, Qvm, Generic };
+enum class Path { QmvRows, Qmv, Tc, Qvm, Generic };
 
 int check_qmm_args(const char* tag, const QmmArgs& a) {
   if (a.dtype != B200Q_F32 && a.dtype != B200Q_F16 && a.dtype != B200Q_BF16)
@@ -54,13 +55,12 @@ int check_qmm_args(const char* tag, const QmmArgs& a) {
   return B200Q_OK;
 }
 
-// B200Q_QMV_IMPL=stream|bulk|mma|tc forces one of the decode kernels where it supports the shape
-// (testing and tuning).
+// B200Q_QMV_IMPL=mma keeps the row-owning decode kernel out of the selection (testing and tuning).
 int qmv_override() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_QMV_IMPL");
-    v = !e ? 0 : (strcmp(e, "bulk") == 0 ? 1 : (strcmp(e, "mma") == 0 ? 2 : (strcmp(e, "tc") == 0 ? 3 : (strcmp(e, "stream") == 0 ? 4 : (strcmp(e, "rows") == 0 ? 5 : 0)))));
+    v = (e && strcmp(e, "mma") == 0) ? 2 : 0;
   }
   return v;
 }
@@ -77,12 +77,8 @@ bool force_tc() {
 Path choose(const QmmArgs& a) {
   const int ov = qmv_override();
   if (force_tc() && qmm_tc_supported(a)) return Path::Tc;  // tuning aid: tensor-memory path for any M
-  if (ov == 3 && qmv_tc_supported(a)) return Path::QmvTc;
-  if (ov == 1 && qmv_bulk_supported(a)) return Path::QmvBulk;
-  if ((ov == 0 || ov == 5) && qmv_rows_supported(a)) return Path::QmvRows;
-  if (qmv_stream_supported(a) && (ov == 4 || (ov == 0 && qmv_stream_profitable(a)))) return Path::QmvStream;
+  if (ov == 0 && qmv_rows_supported(a)) return Path::QmvRows;
   if (qmv_mma_supported(a)) return Path::Qmv;
-  if (ov != 2 && qmv_bulk_supported(a)) return Path::QmvBulk;
   if (qmm_tc_supported(a)) return Path::Tc;
   if (qvm_supported(a)) return Path::Qvm;
   return Path::Generic;
@@ -114,9 +110,6 @@ int run_qmm(const QmmArgs& a, cudaStream_t st) {
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul] null pointer");
   switch (choose(a)) {
     case Path::QmvRows: return qmv_rows(a, st);
-    case Path::QmvStream: return qmv_stream(a, st);
-    case Path::QmvTc: return qmv_tc(a, st);
-    case Path::QmvBulk: return qmv_bulk(a, st);
     case Path::Qmv: return qmv_mma(a, st);
     case Path::Tc: return qmm_tc(a, st);
     case Path::Qvm: return qvm(a, st);
@@ -142,13 +135,7 @@ extern "C" size_t b200q_qmm_workspace_bytes(int dtype, int64_t batch, int64_t M,
                         transpose, 0, nullptr, 0);
   if (!valid_group(group_size) || !valid_bits(bits) || N <= 0 || K <= 0) return 0;
   size_t need = 0;
-  size_t q = qmv_mma_workspace_bytes(a);
-  const size_t qb = qmv_bulk_workspace_bytes(a);
-  q = q > qb ? q : qb;
-  const size_t qt = qmv_tc_workspace_bytes(a);
-  q = q > qt ? q : qt;
-  const size_t qs = qmv_stream_workspace_bytes(a);
-  q = q > qs ? q : qs;
+  const size_t q = qmv_mma_workspace_bytes(a);
   size_t t = qmm_tc_workspace_bytes(a);
   need = q > t ? q : t;
   if (!transpose) {
@@ -175,9 +162,6 @@ extern "C" const char* b200q_qmm_kernel_name(int dtype, int64_t batch, int64_t M
   if (check_qmm_args("quantized_matmul", a)) return "invalid";
   switch (choose(a)) {
     case Path::QmvRows: return "qmv_rows";
-    case Path::QmvStream: return "qmv_stream";
-    case Path::QmvTc: return "qmv_tc";
-    case Path::QmvBulk: return "qmv_bulk";
     case Path::Qmv: return "qmv_mma";
     case Path::Tc: return "qmm_tcgen05";
     case Path::Qvm: return "qvm";
@@ -197,10 +181,14 @@ __global__ void peer_signal_kernel(uint32_t* f0, uint32_t* f1, uint32_t* f2, uin
   *epoch += (uint32_t)n;   // what the local flag must reach before this step's output is complete
   for (int q = 0; q < n; ++q) atomicAdd_system(f[q], 1u);
 }
-__global__ void peer_wait_kernel(const uint32_t* flag, const uint32_t* epoch, uint32_t* status) {
+__global__ void peer_wait_kernel(const uint32_t* flag, const uint32_t* epoch, uint32_t* status, long long limit) {
+  // Launched with programmatic stream serialization: the block may be resident before the kernel
+  // that signals has finished; it reads the epoch only after that kernel has completed, and lets
+  // the next kernel of the stream begin its own prologue at once.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t expected = *epoch;
   const long long t0 = clock64();
-  const long long limit = 2000000000ll;  // about one second of SM clocks
   for (;;) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
@@ -245,10 +233,44 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const T* __restrict__ 
 }  // namespace peer
 }  // namespace b200q
 
+namespace {
+// Bound of b200q_peer_wait in SM clock cycles (default about one second).
+long long g_peer_wait_limit = 2000000000ll;
+
+int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
+                 int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
+                 int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
+                 void* ws, size_t ws_bytes, void* stream);
+}  // namespace
+
+extern "C" void b200q_set_peer_wait_limit_ms(int ms) {
+  g_peer_wait_limit = ms <= 0 ? 2000000000ll : (long long)ms * 2000000ll;   // ~2 GHz SM clock
+}
+
 extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                                  void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M,
                                  int64_t N_local, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
                                  void* stream) {
+  return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, nullptr,
+                      nullptr, nullptr, ws, ws_bytes, stream);
+}
+
+extern "C" int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
+                                        void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M,
+                                        int64_t N_local, int64_t K, int group_size, int bits, uint32_t* const* flag_peers,
+                                        uint32_t* epoch_local, uint32_t* counter_local, void* ws, size_t ws_bytes,
+                                        void* stream) {
+  if (!flag_peers || !epoch_local || !counter_local)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null flag list, epoch or counter");
+  return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, flag_peers,
+                      epoch_local, counter_local, ws, ws_bytes, stream);
+}
+
+namespace {
+int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
+                 int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
+                 int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
+                 void* ws, size_t ws_bytes, void* stream) {
   if (!y_peers || n_peers < 1 || n_peers > kMaxPeers)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] between 1 and %d output buffers are supported (got %d)", kMaxPeers, n_peers);
   if (ld < N_local || col0 < 0 || col0 + N_local > ld)
@@ -261,14 +283,32 @@ extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* 
     a.peers.y[q] = y_peers[q];
   }
   a.peers.n = n_peers; a.peers.ld = ld; a.peers.col0 = col0;
-  if (a.M == 0 || a.N == 0) return B200Q_OK;
-  if (!x || !wq || !scales || !biases) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null pointer");
+  if (flag_peers) {
+    for (int q = 0; q < n_peers; ++q) {
+      if (!flag_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null flag %d", q);
+      a.peers.sig.flags[q] = flag_peers[q];
+    }
+    a.peers.sig.epoch = epoch_local;
+    a.peers.sig.counter = counter_local;
+    a.peers.sig.n = n_peers;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (a.K > 0 && qmv_override() == 0 && qmv_rows_supported(a)) return qmv_rows(a, st);
-  if (a.K > 0 && qmv_mma_supported(a)) return qmv_mma(a, st);
-  if (a.K > 0 && qmm_tc_supported(a)) return qmm_tc(a, st);
+  // the signal goes out even when this rank has nothing to multiply: the other ranks count on it
+  auto signal_only = [&]() -> int {
+    return flag_peers ? b200q_peer_signal(flag_peers, n_peers, epoch_local, stream) : B200Q_OK;
+  };
+  if (a.M == 0 || a.N == 0) return signal_only();
+  if (!x || !wq || !scales || !biases) return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null pointer");
+  if (a.K > 0 && qmv_override() == 0 && qmv_rows_supported(a)) return qmv_rows(a, st);   // signals from its last block
+  if (a.K > 0 && qmv_mma_supported(a)) {
+    a.peers.sig.n = 0;   // the register-path kernel has no fused signal: a launch of its own follows
+    if (int rc = qmv_mma(a, st)) return rc;
+    return signal_only();
+  }
+  if (a.K > 0 && qmm_tc_supported(a)) return qmm_tc(a, st);                                // signals from its last block
   return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
 }
+}  // namespace
 
 extern "C" int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint32_t* epoch_local, void* stream) {
   if (!flag_peers || !epoch_local || n_peers < 1 || n_peers > kMaxPeers)
@@ -285,7 +325,16 @@ extern "C" int b200q_peer_signal(uint32_t* const* flag_peers, int n_peers, uint3
 
 extern "C" int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uint32_t* status, void* stream) {
   if (!flag_local || !epoch_local || !status) return fail(B200Q_ERR_INVALID_ARGUMENT, "[peer_wait] null pointer");
-  peer::peer_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag_local, epoch_local, status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, peer::peer_wait_kernel, flag_local, epoch_local, status, g_peer_wait_limit));
   B200Q_LAUNCH_OK("peer_wait_kernel");
   return B200Q_OK;
 }

@@ -227,12 +227,12 @@ extern "C" int b200q_gather_qmm(const void* x, const uint32_t* wq, const void* s
   return qmm_generic(a, st, &gi);
 }
 
-extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local, const void* scales_local,
-                                        const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
-                                        int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
-                                        int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
-                                        int64_t N, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
-                                        void* stream) {
+namespace {
+int gather_sharded_impl(const void* x, const uint32_t* wq_local, const void* scales_local, const void* biases_local,
+                        const uint32_t* lhs_idx, const uint32_t* rhs_idx, int64_t n_idx, void* const* y_peers, int n_peers,
+                        int self, int dtype, int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                        int64_t N, int64_t K, int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local,
+                        uint32_t* counter_local, void* ws, size_t ws_bytes, void* stream) {
   if (!y_peers || n_peers < 1 || n_peers > kMaxPeers || self < 0 || self >= n_peers)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] between 1 and %d output buffers, one of them this rank's (got %d, self %d)",
                 kMaxPeers, n_peers, self);
@@ -243,13 +243,24 @@ extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local,
                 (long long)e_lo, (long long)(e_lo + E_local), (long long)E_total);
   if (K % group_size != 0 || (K * bits) % 32 != 0)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] The shapes of the weight and scales are incompatible based on bits and group_size");
-  if (n_idx == 0 || M == 0 || N == 0) return B200Q_OK;
+  // the signal goes out even when there is nothing to multiply: the other ranks count on it
+  if (n_idx == 0 || M == 0 || N == 0)
+    return flag_peers ? b200q_peer_signal(flag_peers, n_peers, epoch_local, stream) : B200Q_OK;
   PeerOut peers{};
   for (int q = 0; q < n_peers; ++q) {
     if (!y_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null output buffer %d", q);
     peers.y[q] = y_peers[q];
   }
   peers.n = n_peers; peers.ld = N; peers.col0 = 0;
+  if (flag_peers) {
+    for (int q = 0; q < n_peers; ++q) {
+      if (!flag_peers[q]) return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null flag %d", q);
+      peers.sig.flags[q] = flag_peers[q];
+    }
+    peers.sig.epoch = epoch_local;
+    peers.sig.counter = counter_local;
+    peers.sig.n = n_peers;
+  }
   if (!x || !wq_local || !scales_local || !biases_local || !lhs_idx || !rhs_idx)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null pointer");
   const size_t need = b200q_gather_qmm_workspace_bytes(dtype, n_idx, x_batch, E_total, M, N, K, group_size, bits, 1);
@@ -261,6 +272,32 @@ extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local,
     return fail(B200Q_ERR_UNSUPPORTED, "[gather_qmm_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
   return run_grouped(x, wq_local, scales_local, biases_local, lhs_idx, rhs_idx, n_idx, y_peers[self], &peers, x_batch, E_total,
                      e_lo, E_local, M, N, K, group_size, bits, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int b200q_gather_qmm_sharded(const void* x, const uint32_t* wq_local, const void* scales_local,
+                                        const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
+                                        int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
+                                        int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                                        int64_t N, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
+                                        void* stream) {
+  return gather_sharded_impl(x, wq_local, scales_local, biases_local, lhs_idx, rhs_idx, n_idx, y_peers, n_peers, self, dtype,
+                             x_batch, E_total, e_lo, E_local, M, N, K, group_size, bits, nullptr, nullptr, nullptr, ws,
+                             ws_bytes, stream);
+}
+
+extern "C" int b200q_gather_qmm_sharded_signal(const void* x, const uint32_t* wq_local, const void* scales_local,
+                                               const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
+                                               int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,
+                                               int64_t x_batch, int64_t E_total, int64_t e_lo, int64_t E_local, int64_t M,
+                                               int64_t N, int64_t K, int group_size, int bits,
+                                               uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
+                                               void* ws, size_t ws_bytes, void* stream) {
+  if (!flag_peers || !epoch_local || !counter_local)
+    return fail(B200Q_ERR_INVALID_ARGUMENT, "[gather_qmm_sharded] null flag list, epoch or counter");
+  return gather_sharded_impl(x, wq_local, scales_local, biases_local, lhs_idx, rhs_idx, n_idx, y_peers, n_peers, self, dtype,
+                             x_batch, E_total, e_lo, E_local, M, N, K, group_size, bits, flag_peers, epoch_local,
+                             counter_local, ws, ws_bytes, stream);
 }
 
 // ---------------------------------------------------------------- two chained gather_qmm, one sort

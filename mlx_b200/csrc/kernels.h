@@ -12,11 +12,38 @@ namespace b200q {
 // fused into the epilogue): element (m, n) of the local [M, N] result goes to
 // y[q][m * ld + col0 + n] for every q < n.  n == 0 means the plain output QmmArgs::y.
 constexpr int kMaxPeers = 8;
+// Completion signal fused into a kernel whose output goes to peer buffers: when the last thread
+// block of the grid has finished (and fenced, at system scope) its peer stores, it adds n to the
+// local epoch and 1 to the arrival flag of every rank - what b200q_peer_signal does as a launch of
+// its own.  `counter` is a device word of this rank that starts at zero and is left at zero.
+struct PeerSignal {
+  uint32_t* flags[kMaxPeers];
+  uint32_t* epoch;
+  uint32_t* counter;
+  int n;   // 0: no signal
+};
 struct PeerOut {
   void* y[kMaxPeers];
   int n;
   int64_t ld, col0;
+  PeerSignal sig;
 };
+
+#ifdef __CUDACC__
+// Called by ONE thread of every thread block after all peer stores of the block have been issued
+// and ordered before this thread (a block- or warp-wide barrier).
+__device__ __forceinline__ void peer_signal_tail(const PeerSignal& ps) {
+  if (ps.n == 0) return;
+  __threadfence_system();
+  const unsigned old = atomicAdd(ps.counter, 1u);
+  if (old == gridDim.x * gridDim.y * gridDim.z - 1) {
+    *ps.counter = 0;
+    __threadfence_system();
+    *ps.epoch += (uint32_t)ps.n;   // what the local flag must reach before this step's output is complete
+    for (int q = 0; q < ps.n; ++q) atomicAdd_system(ps.flags[q], 1u);
+  }
+}
+#endif
 
 struct QmmArgs {
   const void* x;
@@ -81,22 +108,6 @@ void set_weights_constant(int on);
 bool qvm_supported(const QmmArgs& a);
 size_t qvm_workspace_bytes(const QmmArgs& a);
 int qvm(const QmmArgs& a, cudaStream_t st);
-
-// qmv_stream.cu : decode path for 4-bit weights (TMA ring, ldmatrix, exact factorised form)
-bool qmv_stream_supported(const QmmArgs& a);
-bool qmv_stream_profitable(const QmmArgs& a);   // large enough to beat qmv_mma
-size_t qmv_stream_workspace_bytes(const QmmArgs& a);
-int qmv_stream(const QmmArgs& a, cudaStream_t st);
-
-// qmv_bulk.cu : decode path for 4-bit weights (bulk-copy staged, exact factorised form)
-bool qmv_bulk_supported(const QmmArgs& a);
-size_t qmv_bulk_workspace_bytes(const QmmArgs& a);
-int qmv_bulk(const QmmArgs& a, cudaStream_t st);
-
-// qmv_tc.cu : decode path on tcgen05 (thread-per-row unpack into TMEM, per-group accumulators)
-bool qmv_tc_supported(const QmmArgs& a);
-size_t qmv_tc_workspace_bytes(const QmmArgs& a);
-int qmv_tc(const QmmArgs& a, cudaStream_t st);
 
 // qmm_tcgen05.cu : prefill path (TMA + tcgen05 + TMEM), transpose only, bf16
 bool qmm_tc_supported(const QmmArgs& a);

@@ -96,6 +96,7 @@ struct TcParams {
   __nv_bfloat16* y_out[kMaxPeers];
   int n_out;
   long long ld, col0;
+  PeerSignal sig;    // completion signal towards the ranks that receive y (n == 0: none)
   uint32_t* status;
   int M, N, K;
   int NT;            // tokens per tile (multiple of 16, <= 256)
@@ -193,6 +194,10 @@ __device__ __forceinline__ TileCoord tile_coord(const TcParams& p, int tile) {
   return t;
 }
 
+#ifdef B200Q_PROFILE
+__device__ uint32_t g_tc_prof[64];
+#endif
+
 template <int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -214,9 +219,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef B200Q_PROFILE
-  // Profile builds (plain mode only): CTA 0 leaves per-role wait cycles / 16 in the 256 bytes
-  // before the status word; the caller's workspace must have that room.
-  uint32_t* dbg = p.status - 64;
+  // Tuning builds (plain mode only): thread block 0 leaves per-role wait cycles / 16 in a buffer of
+  // its own (g_tc_prof), which a test harness reads back with cudaMemcpyFromSymbol.
+  uint32_t* dbg = g_tc_prof;
   long long pw0 = 0, pw1 = 0, pw2 = 0, pt = 0;
   const long long prof_entry = clock64();
 #define TC_T0() pt = clock64()
@@ -466,6 +471,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   tcgen05_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicMax(&p.status[0], 3u);
+  if (threadIdx.x == 0) peer_signal_tail(p.sig);   // every store of the block precedes the barrier above
   if (warp == 1) {
     tcgen05_fence_after();
     tcgen05_dealloc(tmem_base, kTmemCols);
@@ -569,6 +575,7 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
   if (a.peers.n > 0) {
     p.n_out = a.peers.n; p.ld = a.peers.ld; p.col0 = a.peers.col0;
     for (int q = 0; q < a.peers.n; ++q) p.y_out[q] = (__nv_bfloat16*)a.peers.y[q];
+    p.sig = a.peers.sig;
   } else {
     p.n_out = 1; p.ld = a.N; p.col0 = 0; p.y_out[0] = (__nv_bfloat16*)a.y;
   }
@@ -621,6 +628,7 @@ int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
   if (a.peers.n > 0) {
     p.n_out = a.peers.n;
     for (int q = 0; q < a.peers.n; ++q) p.y_out[q] = (__nv_bfloat16*)a.peers.y[q];
+    p.sig = a.peers.sig;
   } else {
     p.n_out = 1; p.y_out[0] = (__nv_bfloat16*)a.y;
   }

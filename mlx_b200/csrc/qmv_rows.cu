@@ -24,8 +24,10 @@
 //    * 2^-133; one shift by 8 brings the other two bytes down.  The integer processing pipe that
 //    does the unpacking is what bounds this kernel, and this form needs 5 operations per 8 four-bit
 //    weights (3 per 4 eight-bit weights, 9 per 16 two-bit weights) and no offset correction.
-//    x is pre-multiplied by 2^64 (and 2^60 where the field sits four bits up) when it is put into
-//    registers; the reducer multiplies the sums by 2^69.  (|x| >= 2^64 would overflow; see b200q.h.)
+//    To keep the products inside fp32's range whatever the magnitude of x, every token row of a
+//    warp's K slice is multiplied by a power of two that brings its largest element to about 2^64
+//    (less where the field sits some bits up) when it is put into registers, and the warp's sums
+//    are multiplied back by the matching power of two before they leave the warp: exact.
 //    Scales are applied per group to fp32 group sums, the biases come back through one small MMA
 //    against the group sums of x:  y = sum_g s_g * (sum_k x_k q_k) + sum_g b_g * (sum_k x_k).
 //    Four independent accumulation chains per warp hide the mma.sync latency.
@@ -130,6 +132,7 @@ __device__ __forceinline__ uint2 ldg_nc_u64(const void* p) {
 __device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 __device__ __forceinline__ float sum_bf16x2(uint32_t v) { return bf16lo(v) + bf16hi(v); }
+__device__ __forceinline__ float asum_bf16x2(uint32_t v) { return fabsf(bf16lo(v)) + fabsf(bf16hi(v)); }
 
 __host__ __device__ constexpr int cmin(int a, int b) { return a < b ? a : b; }
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
@@ -156,6 +159,7 @@ struct RowsParams {
   __nv_bfloat16* y[kMaxPeers];
   int n_out;
   long long ld, col0;
+  PeerSignal sig;       // completion signal towards the ranks that receive y (n == 0: none)
   int M, N, K;
   int nblk8;            // ceil(N / 8)
   int nph;              // phases over K
@@ -184,13 +188,11 @@ __device__ __forceinline__ void unpack_word(uint32_t w, uint32_t* P) {
     P[4] = u & 0x00030003u; P[5] = u & 0x000C000Cu; P[6] = u & 0x00300030u; P[7] = u & 0x00C000C0u;
   }
 }
-// bf16x2 constant that x pair i is multiplied with: 2^64 divided by the position weight of field i.
+// Binary places by which field i of a word sits above bit 0 of its byte: x pair i is scaled down by
+// as many powers of two.
 template <int BITS>
-__device__ __forceinline__ constexpr uint32_t xscale(int i) {
-  // 2^64 = 0x5F80, 2^62 = 0x5E80, 2^60 = 0x5D80, 2^58 = 0x5C80
-  if (BITS == 4) return (i & 1) ? 0x5D805D80u : 0x5F805F80u;
-  if (BITS == 8) return 0x5F805F80u;
-  return (i & 3) == 0 ? 0x5F805F80u : ((i & 3) == 1 ? 0x5E805E80u : ((i & 3) == 2 ? 0x5D805D80u : 0x5C805C80u));
+__host__ __device__ constexpr int field_shift(int i) {
+  return BITS == 4 ? ((i & 1) ? 4 : 0) : (BITS == 8 ? 0 : 2 * (i & 3));
 }
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
   uint16_t v;
@@ -211,7 +213,7 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   constexpr int NGW = C::NGW, NP = C::NP, UG = C::UG, UW = C::UW, KW = C::KW;
   extern __shared__ __align__(1024) unsigned char smem[];
   // header: [0, 128) "stage landed" barriers | [128, 256) "stage consumed" barriers |
-  //         [256, 288) "partial buffer free" barriers | 320: abort flag
+  //         [256, 288) "partial buffer free" barriers | 320: abort flag | [512, 1024) output tile
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t full0 = smem_base, done0 = smem_base + 128, pfree0 = smem_base + 256;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 320);
@@ -373,27 +375,39 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           }
         }
         if (final_phase) {
+          // transpose the 16 rows x 8*MT tokens through shared memory so that every lane stores 16
+          // contiguous bytes of one token's row of y
           const int row0 = (b0 + 2 * rrg) * 8;
+          __nv_bfloat16* yt = reinterpret_cast<__nv_bfloat16*>(smem + 512);   // [16 tokens][16 rows]
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
+          for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int row = row0 + g + (c >> 1) * 8;
-              const int tok = mt * 8 + 2 * t + (c & 1);
-              if (row < row_end && tok < p.M) {
-                // undo the 2^-133 of the subnormal weights and the 2^64 of x
-                const __nv_bfloat16 o = __float2bfloat16_rn(sum[mt][c] * 0x1p69f);
-                const long long at = (long long)tok * p.ld + p.col0 + row;
-                p.y[0][at] = o;
-                for (int q = 1; q < p.n_out; ++q) p.y[q][at] = o;
+            for (int c = 0; c < 4; ++c)
+              yt[(mt * 8 + 2 * t + (c & 1)) * 16 + g + (c >> 1) * 8] = __float2bfloat16_rn(sum[mt][c]);
+          __syncwarp();
+          const int tok = lane >> 1, r8 = row0 + (lane & 1) * 8;
+          if (tok < p.M && r8 < row_end) {
+            const uint4 v = *reinterpret_cast<const uint4*>(yt + tok * 16 + (lane & 1) * 8);
+            const long long at = (long long)tok * p.ld + p.col0 + r8;
+            const bool vec = r8 + 8 <= row_end && ((at | p.ld) & 7) == 0;
+            for (int q = 0; q < p.n_out; ++q) {
+              __nv_bfloat16* dst = p.y[q] + at;
+              if (vec && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                *reinterpret_cast<uint4*>(dst) = v;
+              } else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+                for (int i = 0; i < 8 && r8 + i < row_end; ++i) dst[i] = e[i];
               }
             }
           }
+          __syncwarp();
         }
         if (++rrg == nrg) { rrg = 0; ++rph; }
         RP_MARK(6 + 2 * red);
       }
       RP_MARK(30);
+      __syncwarp();   // all of this block's stores to y were issued by this warp
+      if (lane == 0) peer_signal_tail(p.sig);
 #ifdef B200Q_ROWS_PROFILE
       if (lane == 0) {
         unsigned long long gt;
@@ -416,7 +430,8 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   asm volatile("griddepcontrol.wait;" ::: "memory");
   RP_MARK(2);
   uint32_t X[UW][MT][NP];         // B fragments of this warp's K slice, pre-scaled
-  uint32_t sx_hi[MT], sx_lo[MT];  // 2^-69 * group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)
+  uint32_t sx_hi[MT], sx_lo[MT];  // scaled group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)
+  float unscale[MT][2];           // per output token (2t, 2t+1 of tile mt): what brings the warp's sums back to true units / 2^69
   uint32_t woff[UW / 2];          // this lane's ldmatrix addresses inside a stage
   uint32_t soff = 0;              // scale of (row g, first group of the slice) inside a stage
   int cnt = 0;
@@ -437,10 +452,13 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     // groups lie inside one unit; the same entry of row g + 8 is 1024 bytes further on
     soff = (uint32_t)(p.nch + ((2 * g0) >> 7)) * 2048 + g * 128 + (((((2 * g0) >> 4) & 7) ^ g) << 4) + ((2 * g0) & 15);
     float sx[NGW][MT];
+    float asum[MT];   // sum of |x| per token: an upper bound of the largest element that costs no integer operations
 #pragma unroll
-    for (int j = 0; j < NGW; ++j)
+    for (int mt = 0; mt < MT; ++mt) {
+      asum[mt] = 0.0f;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) sx[j][mt] = 0.0f;
+      for (int j = 0; j < NGW; ++j) sx[j][mt] = 0.0f;
+    }
     // unit i of the slice: 4 * KW consecutive k, of which this lane owns KW starting at t * KW
     const long long k0 = (long long)(p.ph_g0[ph] + g0) * G + t * KW;
 #pragma unroll
@@ -450,35 +468,59 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int tok = mt * 8 + g;
         const bool live = i < cnt * UG && tok < p.M;
         const __nv_bfloat16* xp = p.x + (long long)tok * p.K + k0 + i * (4 * KW);
-        uint32_t r[NP];   // pair i = (x_i, x_{i + NP})
+        // pair q = (x_q, x_{q + NP}), the order the unpack delivers the fields in
         if constexpr (BITS == 8) {
           uint2 v = make_uint2(0, 0);
           if (live) v = ldg_nc_u64(xp);
           sx[i / UG][mt] += sum_bf16x2(v.x) + sum_bf16x2(v.y);
-          r[0] = __byte_perm(v.x, v.y, 0x5410); r[1] = __byte_perm(v.x, v.y, 0x7632);
+          asum[mt] += asum_bf16x2(v.x) + asum_bf16x2(v.y);
+          X[i][mt][0] = __byte_perm(v.x, v.y, 0x5410); X[i][mt][1] = __byte_perm(v.x, v.y, 0x7632);
         } else if constexpr (BITS == 4) {
           uint4 v = make_uint4(0, 0, 0, 0);
           if (live) v = ldg_nc_u128(xp);
           sx[i / UG][mt] += (sum_bf16x2(v.x) + sum_bf16x2(v.y)) + (sum_bf16x2(v.z) + sum_bf16x2(v.w));
-          r[0] = __byte_perm(v.x, v.z, 0x5410); r[1] = __byte_perm(v.x, v.z, 0x7632);
-          r[2] = __byte_perm(v.y, v.w, 0x5410); r[3] = __byte_perm(v.y, v.w, 0x7632);
+          asum[mt] += (asum_bf16x2(v.x) + asum_bf16x2(v.y)) + (asum_bf16x2(v.z) + asum_bf16x2(v.w));
+          X[i][mt][0] = __byte_perm(v.x, v.z, 0x5410); X[i][mt][1] = __byte_perm(v.x, v.z, 0x7632);
+          X[i][mt][2] = __byte_perm(v.y, v.w, 0x5410); X[i][mt][3] = __byte_perm(v.y, v.w, 0x7632);
         } else {
           uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
           if (live) { a = ldg_nc_u128(xp); b = ldg_nc_u128(xp + 8); }
           sx[i / UG][mt] += (sum_bf16x2(a.x) + sum_bf16x2(a.y)) + (sum_bf16x2(a.z) + sum_bf16x2(a.w)) +
                             (sum_bf16x2(b.x) + sum_bf16x2(b.y)) + (sum_bf16x2(b.z) + sum_bf16x2(b.w));
-          r[0] = __byte_perm(a.x, b.x, 0x5410); r[1] = __byte_perm(a.x, b.x, 0x7632);
-          r[2] = __byte_perm(a.y, b.y, 0x5410); r[3] = __byte_perm(a.y, b.y, 0x7632);
-          r[4] = __byte_perm(a.z, b.z, 0x5410); r[5] = __byte_perm(a.z, b.z, 0x7632);
-          r[6] = __byte_perm(a.w, b.w, 0x5410); r[7] = __byte_perm(a.w, b.w, 0x7632);
+          asum[mt] += (asum_bf16x2(a.x) + asum_bf16x2(a.y)) + (asum_bf16x2(a.z) + asum_bf16x2(a.w)) +
+                      (asum_bf16x2(b.x) + asum_bf16x2(b.y)) + (asum_bf16x2(b.z) + asum_bf16x2(b.w));
+          X[i][mt][0] = __byte_perm(a.x, b.x, 0x5410); X[i][mt][1] = __byte_perm(a.x, b.x, 0x7632);
+          X[i][mt][2] = __byte_perm(a.y, b.y, 0x5410); X[i][mt][3] = __byte_perm(a.y, b.y, 0x7632);
+          X[i][mt][4] = __byte_perm(a.z, b.z, 0x5410); X[i][mt][5] = __byte_perm(a.z, b.z, 0x7632);
+          X[i][mt][6] = __byte_perm(a.w, b.w, 0x5410); X[i][mt][7] = __byte_perm(a.w, b.w, 0x7632);
         }
-#pragma unroll
-        for (int q = 0; q < NP; ++q) X[i][mt][q] = mul_bf16x2(r[q], xscale<BITS>(q));
       }
     }
-    // group sums over the quad, then lane t keeps groups 2t and 2t+1 (the k slots it feeds)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
+      // sum of |x| of token g over this warp's slice (lane's registers, then the quad): at least the
+      // largest element, at most 128 times it
+      float am = asum[mt];
+      am += __shfl_xor_sync(0xFFFFFFFFu, am, 1);
+      am += __shfl_xor_sync(0xFFFFFFFFu, am, 2);
+      const uint32_t m = __float_as_uint(am);
+      // E: x is multiplied by 2^E so that its largest element lands at or below 2^65
+      int E = 191 - (int)((m >> 23) & 0xFF);
+      E = E < -62 ? -62 : (E > 120 ? 120 : E);
+      const uint32_t sc = (uint32_t)(127 + E) << 7;   // bf16 bits of 2^E
+      const uint32_t sc2 = sc | (sc << 16);
+#pragma unroll
+      for (int i = 0; i < UW; ++i)
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+          X[i][mt][q] = mul_bf16x2(X[i][mt][q], sc2 - (uint32_t)field_shift<BITS>(q) * 0x00800080u);
+      // the weights come out as field * 2^-133: the sums of this token are true value * 2^(E - 133);
+      // 2^(64 - E) is applied when the sums leave the warp, 2^69 with it
+      const float un = __uint_as_float((uint32_t)(127 + 64 - E) << 23);
+      unscale[mt][0] = __shfl_sync(0xFFFFFFFFu, un, (2 * t) * 4);
+      unscale[mt][1] = __shfl_sync(0xFFFFFFFFu, un, (2 * t + 1) * 4);
+      // group sums over the quad, in the same units; lane t keeps groups 2t and 2t+1 (the k slots it feeds)
+      const float down = __uint_as_float((uint32_t)(127 + E - 64) << 23) * 0x1p-69f;
       float e0 = 0.0f, e1 = 0.0f;
 #pragma unroll
       for (int j = 0; j < NGW; ++j) {
@@ -489,7 +531,7 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           if (j & 1) e1 = v; else e0 = v;
         }
       }
-      e0 *= 0x1p-69f; e1 *= 0x1p-69f;   // the scale every other term of the sums carries
+      e0 *= down; e1 *= down;
       const uint32_t hi = pack_bf16x2(e0, e1);
       sx_hi[mt] = hi;
       sx_lo[mt] = pack_bf16x2(e0 - bf16lo(hi), e1 - bf16hi(hi));
@@ -596,9 +638,10 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     {
       const uint32_t pa = pb_mine + (uint32_t)pbi * (kConsumers * MT * 512);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(pa + mt * 512), "f"(out[mt][0]), "f"(out[mt][1]),
-                     "f"(out[mt][2]), "f"(out[mt][3]) : "memory");
+      for (int mt = 0; mt < MT; ++mt)   // back to true units on the way out (two exact multiplications)
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(pa + mt * 512),
+                     "f"(out[mt][0] * 0x1p69f * unscale[mt][0]), "f"(out[mt][1] * 0x1p69f * unscale[mt][1]),
+                     "f"(out[mt][2] * 0x1p69f * unscale[mt][0]), "f"(out[mt][3] * 0x1p69f * unscale[mt][1]) : "memory");
     }
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(done0 + 8 * slot);   // release: the partial tile is visible to the reducer
@@ -680,7 +723,7 @@ bool fill_plan(const QmmArgs& a, RowsPlan& pl) {
   pl.grid = p.nblk8 < sms ? p.nblk8 : sms;
   const int max_blk = (p.nblk8 + pl.grid - 1) / pl.grid;
   const int max_rg = (max_blk + 1) / 2 + 1;
-  size_t off = 512;
+  size_t off = 1024;   // barriers, abort flag, the reducer's 512-byte output tile
   p.off_tile = (uint32_t)off;
   if (p.nph > 1) off += (size_t)max_rg * MT * 512;
   p.off_pbuf = (uint32_t)off;
@@ -723,6 +766,7 @@ RowsPlan make_plan(const QmmArgs& a) {
   if (a.peers.n > 0) {
     p.n_out = a.peers.n; p.ld = a.peers.ld; p.col0 = a.peers.col0;
     for (int q = 0; q < a.peers.n; ++q) p.y[q] = (__nv_bfloat16*)a.peers.y[q];
+    p.sig = a.peers.sig;
   } else {
     p.n_out = 1; p.ld = a.N; p.col0 = 0; p.y[0] = (__nv_bfloat16*)a.y;
   }

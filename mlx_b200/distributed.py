@@ -132,7 +132,7 @@ class PeerOutput:
             raise ValueError("at most 8 ranks can share output buffers")
         self.m_max, self.n_total = m_max, n_total
         self.buf_bytes = (m_max * n_total * 2 + 255) // 256 * 256
-        total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word and (at +128) the epoch
+        total = self.N_BUF * self.buf_bytes + 256          # outputs, then the flag word, the epoch (+128), the block counter (+192)
         # Every rank walks the same sequence of collectives even when a local step fails; the failure
         # is agreed on at the end, so that all ranks raise together instead of some of them hanging.
         err = None
@@ -172,7 +172,9 @@ class PeerOutput:
             raise RuntimeError(f"[PeerOutput] peer-mapped output buffers are not available on every rank: {err}")
         self.flag = [b + self.N_BUF * self.buf_bytes for b in self.base]
         self.epoch = self._own + self.N_BUF * self.buf_bytes + 128
+        self.counter = self._own + self.N_BUF * self.buf_bytes + 192
         self.step = 0
+        self._ws = None   # workspace of the last call: its status word says whether a wait ran out
         # torch views of the local buffers, made once (nothing is created during stream capture)
         self._views = [torch.as_tensor(_DevMem(self._own + i * self.buf_bytes, m_max * n_total), device="cuda")
                        .view(torch.bfloat16).view(m_max, n_total) for i in range(self.N_BUF)]
@@ -188,6 +190,14 @@ class PeerOutput:
         """This rank's copy of the gathered [m, n_total] result in buffer `buf`."""
         return self._views[buf][:m]
 
+    def check(self) -> None:
+        """Synchronises the current stream and raises ops.DeviceStatusError if the last exchange
+        did not complete (a peer lagged behind the bounded wait, code 6) or a kernel gave up on one
+        of its own waits.  The exchange functions below never synchronise: call this before results
+        are consumed where a rank may stall for longer than the wait's bound."""
+        if self._ws is not None:
+            ops.read_workspace_status(self._ws, torch.cuda.current_stream(self._ws.device).cuda_stream, "peer exchange")
+
     def close(self):
         if self._own is None:
             return
@@ -202,7 +212,8 @@ class PeerOutput:
 
 def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tensor, out: PeerOutput) -> torch.Tensor:
     """y = x @ dequant(W)^T for the full W, every rank holding only its rows: one matmul launch
-    whose epilogue stores to all ranks, one flag update, one bounded wait.  x: [M, K] bf16 CUDA,
+    whose epilogue stores to all ranks and whose last thread block updates the flags, and one
+    bounded wait (`out.check()` tells whether it ran out).  x: [M, K] bf16 CUDA,
     the same on every rank.  Returns this rank's [M, N] view (valid until the buffer is used again
     two calls later)."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
@@ -218,11 +229,12 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
     st = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
     buf = out.step % out.N_BUF
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
-    _lib.check(lib.b200q_qmm_sharded(vp(x), vp(layer.weight), vp(layer.scales), vp(layer.biases), out.y_ptrs(buf),
-                                     out.world, out.n_total, out.rank * layer.n_local, dt, M, layer.n_local, K,
-                                     layer.group_size, layer.bits, vp(ws), ws.numel(), st))
-    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, ctypes.c_void_p(out.epoch), st))
+    _lib.check(lib.b200q_qmm_sharded_signal(vp(x), vp(layer.weight), vp(layer.scales), vp(layer.biases), out.y_ptrs(buf),
+                                            out.world, out.n_total, out.rank * layer.n_local, dt, M, layer.n_local, K,
+                                            layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
+                                            ctypes.c_void_p(out.counter), vp(ws), ws.numel(), st))
     out.step += 1
+    out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
     _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     return out.local(buf, M)
@@ -252,11 +264,13 @@ def sharded_gather_qmm(x: torch.Tensor, w_local: torch.Tensor, scales_local: tor
     st = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
     buf = out.step % out.N_BUF
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
-    _lib.check(lib.b200q_gather_qmm_sharded(vp(x), vp(w_local), vp(scales_local), vp(biases_local), vp(lhs32), vp(rhs32),
-                                            n_idx, out.y_ptrs(buf), out.world, out.rank, dt, B, n_experts, e_lo, E_local,
-                                            M, N, K, group_size, bits, vp(ws), ws.numel(), st))
-    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), out.world, ctypes.c_void_p(out.epoch), st))
+    _lib.check(lib.b200q_gather_qmm_sharded_signal(vp(x), vp(w_local), vp(scales_local), vp(biases_local), vp(lhs32),
+                                                   vp(rhs32), n_idx, out.y_ptrs(buf), out.world, out.rank, dt, B, n_experts,
+                                                   e_lo, E_local, M, N, K, group_size, bits, out.flag_ptrs(),
+                                                   ctypes.c_void_p(out.epoch), ctypes.c_void_p(out.counter), vp(ws),
+                                                   ws.numel(), st))
     out.step += 1
+    out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
     _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     return out.local(buf, n_idx * M).view(n_idx, M, N)
@@ -334,10 +348,11 @@ def sharded_matmul_allreduce(layer: QuantizedShardedToAllLinear, x: torch.Tensor
     slot_bytes = M * N * 2
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
     ys = (ctypes.c_void_p * R)(*[b + buf * out.buf_bytes + out.rank * slot_bytes for b in out.base])
-    _lib.check(lib.b200q_qmm_sharded(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M, N, K,
-                                     layer.group_size, layer.bits, vp(ws), ws.numel(), st))
-    _lib.check(lib.b200q_peer_signal(out.flag_ptrs(), R, ctypes.c_void_p(out.epoch), st))
+    _lib.check(lib.b200q_qmm_sharded_signal(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M,
+                                            N, K, layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
+                                            ctypes.c_void_p(out.counter), vp(ws), ws.numel(), st))
     out.step += 1
+    out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
     _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
     y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)

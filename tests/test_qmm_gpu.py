@@ -59,20 +59,20 @@ def test_golden_qmm(dtype, g, bits):
 @pytest.mark.parametrize("g", (32, 64, 128))
 @pytest.mark.parametrize("M", (1, 3, 8, 9, 16))
 def test_qmv_all_widths(bits, g, M):
-    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_rows", "qmv_stream", "qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, 512, 1024, g, bits, seed=bits * 10 + M, expect_kernel=("qmv_rows", "qmv_mma"))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 14336, 4096), (7, 67, 256), (2, 8, 128), (16, 1000, 2048),
                                    (5, 28672, 8192), (13, 4104, 4096), (16, 24, 128)])
 def test_qmv_shapes_4bit(M, N, K):
-    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_rows", "qmv_stream", "qmv_mma", "qmv_bulk"))
+    run_case("bf16", M, N, K, 64, 4, seed=M + N, expect_kernel=("qmv_rows", "qmv_mma"))
 
 
 @pytest.mark.parametrize("M,g", [(1, 64), (2, 32), (4, 128)])
-def test_qmv_stream_is_default_for_large_small_batch(M, g):
-    """Large 4-bit matrices with M <= 4 go to the TMA-ring kernel by default (elsewhere it is only
-    reachable through B200Q_QMV_IMPL=stream, see the subprocess test below)."""
-    run_case("bf16", M, 28672 - 96, 8192, g, 4, seed=M + g, expect_kernel=("qmv_rows", "qmv_stream"))
+def test_row_owning_kernel_on_a_large_ragged_matrix(M, g):
+    """Large matrices whose row count is not a multiple of the 16-row stage (the last stage of the
+    last thread block is zero-filled past N)."""
+    run_case("bf16", M, 28672 - 96 + 5, 8192, g, 4, seed=M + g, expect_kernel=("qmv_rows",))
 
 
 def test_qmv_repeated_calls_reuse_scratch():
@@ -147,11 +147,10 @@ def test_mixed_dtype_promotes_to_float32():
     assert ok, rel
 
 
-@pytest.mark.parametrize("impl", ("bulk", "tc", "mma", "stream"))
-def test_qmv_alternative_kernels_in_subprocess(impl):
-    """The bulk-copy staged (mma.sync) and the tensor-memory (tcgen05) decode kernels are selected
-    with B200Q_QMV_IMPL=bulk|tc; run a few shapes through each in a child process (the override is
-    read once per process)."""
+def test_register_path_decode_kernel_in_subprocess():
+    """B200Q_QMV_IMPL=mma keeps the row-owning kernel out of the selection, so the register-path
+    kernel (the one that also serves bits 3/5/6 and ragged K) runs the 4-bit shapes; the override is
+    read once per process, hence the child process."""
     import subprocess
     import sys
     code = r'''
@@ -159,11 +158,8 @@ import sys
 sys.path.insert(0, "tests")
 import torch, oracle as O, mlx_b200 as mb
 from util import from_torch, make_w, make_x, qmm_close, to_torch, u32_to_torch
-for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048, 32), (13, 4104, 4096, 128), (5, 520, 8192, 64)]:
-    # the last shape exceeds the tensor-memory variant's shared-memory budget and falls back to the
-    # default kernel ON THE SAME WORKSPACE: every kernel must leave the workspace zeroed
-    name = mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4)
-    assert name == "qmv_" + sys.argv[1] or (K == 8192 and name == "qmv_mma"), name
+for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048, 32), (13, 4104, 4096, 128)]:
+    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, g, 4) == "qmv_mma"
     wq, s, b = O.quantize(make_w(N, (N, K), "bf16"), g, 4, "bf16")
     x = make_x(M, (M, K), "bf16")
     ref = O.qmm_f32_from(x, wq, s, b, "bf16", transpose=True, group_size=g, bits=4)
@@ -171,12 +167,47 @@ for (M, N, K, g) in [(1, 4096, 4096, 64), (16, 14336, 4096, 64), (8, 1000, 2048,
         y = mb.quantized_matmul(to_torch(x, "bf16"), u32_to_torch(wq), to_torch(s, "bf16"), to_torch(b, "bf16"), group_size=g, bits=4)
     ok, rel = qmm_close(O.to_f32(from_torch(y), "bf16"), ref)
     assert ok, (M, N, K, g, rel)
-print("bulk-ok")
+print("mma-ok")
 '''
-    env = dict(os.environ, B200Q_QMV_IMPL=impl)
+    env = dict(os.environ, B200Q_QMV_IMPL="mma")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    res = subprocess.run([sys.executable, "-c", code, impl], cwd=root, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0 and "bulk-ok" in res.stdout, res.stdout + res.stderr
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "mma-ok" in res.stdout, res.stdout + res.stderr
+
+
+@pytest.mark.parametrize("bits,g", [(2, 64), (2, 128), (4, 32), (4, 64), (4, 128), (8, 32), (8, 64), (8, 128)])
+@pytest.mark.parametrize("M", (1, 7, 8, 9, 16))
+def test_row_owning_kernel_every_instantiation(bits, g, M):
+    """Every (bits, group, token-tile) instantiation of the row-owning kernel, on a K that needs two
+    phases for some of them and a row count that leaves the last 16-row stage half empty."""
+    run_case("bf16", M, 2504, 4096, g, bits, seed=bits + g + M, expect_kernel=("qmv_rows",))
+
+
+@pytest.mark.parametrize("M,N,K,bits,g", [(3, 4096, 14336, 4, 64), (16, 4096, 14336, 4, 64), (2, 1024, 28672, 8, 64),
+                                          (16, 520, 7168, 4, 32), (5, 136, 16384, 2, 128)])
+def test_row_owning_kernel_long_k_phases(M, N, K, bits, g):
+    """K longer than one phase of the 16 K slices: phases of different widths, running sums in shared memory."""
+    run_case("bf16", M, N, K, g, bits, seed=M + K, expect_kernel=("qmv_rows",))
+
+
+def test_row_owning_kernel_extreme_activations():
+    """x is pre-scaled by 2^64 inside the kernel: values up to 2^60 and down to 2^-60 must survive."""
+    dtype, M, N, K = "bf16", 4, 256, 1024
+    w = make_w(7, (N, K), dtype)
+    wq, s, b = O.quantize(w, 64, 4, dtype)
+    rng = np.random.default_rng(8)
+    xf = rng.standard_normal((M, K)).astype(np.float32)
+    xf[0] *= 2.0 ** 60
+    xf[1] *= 2.0 ** -60
+    xf[2, ::7] *= 2.0 ** 40
+    x = O.to_dtype(xf, dtype)
+    ref = O.qmm_f32_from(x, wq, s, b, dtype, transpose=True, group_size=64, bits=4)
+    y = mb.quantized_matmul(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype))
+    assert mb.qmm_kernel_name(torch.bfloat16, M, N, K, 64, 4) == "qmv_rows"
+    got = O.to_f32(from_torch(y), dtype)
+    for m in range(M):   # rows differ by 120 binades: compare row by row
+        ok, rel = qmm_close(got[m:m + 1], ref[m:m + 1])
+        assert ok, (m, rel)
 
 
 # ---- prefill path (TMA + tcgen05 + TMEM) -------------------------------------------------
@@ -239,7 +270,7 @@ def test_qvm_then_transposed_decode_share_workspace():
     accumulate into the same workspace."""
     for _ in range(2):
         run_case("bf16", 2, 4096, 2048, 64, 4, transpose=False, seed=11, expect_kernel=("qvm",))
-        run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_rows", "qmv_mma", "qmv_stream"))
+        run_case("bf16", 16, 1000, 2048, 64, 4, seed=12, expect_kernel=("qmv_rows", "qmv_mma"))
 
 
 # ---- host-buffer entry point -------------------------------------------------------------------
@@ -272,3 +303,38 @@ def test_qmm_host_buffers(pinned, M):
         torch.cuda.synchronize()
     ok, rel = qmm_close(O.to_f32(y_host.view(torch.int16).numpy().view(np.uint16), "bf16"), ref)
     assert ok, rel
+
+
+def test_quantize_then_matmul_on_a_reused_buffer():
+    """The decode kernels start under programmatic dependent launch.  By default they request the
+    weights only after the previous kernel of the stream has finished, so a quantize (or any other
+    producer of wq / scales / biases) directly in front of the matmul, writing into buffers the
+    previous matmul has just read, gives the same bits as a fully serialised run."""
+    dtype, M, N, K, g, bits = "bf16", 16, 4096, 4096, 64, 4
+    x = to_torch(make_x(5, (M, K), dtype), dtype)
+    ws = [to_torch(make_w(40 + i, (N, K), dtype), dtype) for i in range(3)]
+    wq = torch.empty(N, K * bits // 32, dtype=torch.uint32, device="cuda")
+    s = torch.empty(N, K // g, dtype=torch.bfloat16, device="cuda")
+    b = torch.empty_like(s)
+    import ctypes
+    from mlx_b200 import _lib
+    lib = _lib.load()
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    need = max(int(lib.b200q_qmm_workspace_bytes(_lib.BF16, 1, M, N, K, g, bits, 1)), 256)
+    wsp = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    outs, refs = [], []
+    for rnd in range(6):
+        w = ws[rnd % 3]
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        assert lib.b200q_quantize(P(w), _lib.BF16, N, K, g, bits, P(wq), P(s), P(b), st) == 0
+        assert lib.b200q_qmm(P(x), P(wq), P(s), P(b), P(y), _lib.BF16, 1, M, N, K, g, bits, 1, 0, P(wsp), wsp.numel(), st) == 0
+        outs.append(y)
+    torch.cuda.synchronize()
+    for rnd in range(6):   # the serialised reference: synchronise between the two calls
+        q = mb.quantize(ws[rnd % 3], g, bits)
+        torch.cuda.synchronize()
+        refs.append(mb.quantized_matmul(x, *q, group_size=g, bits=bits))
+        torch.cuda.synchronize()
+    for y, r in zip(outs, refs):
+        assert torch.equal(y.view(torch.int16), r.view(torch.int16))
