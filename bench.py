@@ -428,10 +428,12 @@ def main():
     layers = [QuantizedAllToShardedLinear(q, s, b, GROUP, BITS, rank=rank, world=world, already_sharded=True)
               for (q, s, b) in weights] if world > 1 else None
 
-    def step(i):
-        """One step: the matmul on this rank's rows and, at N > 1, the exchange; returns the full [M, N]."""
+    def step(i, chained=False):
+        """One step: the matmul on this rank's rows and, at N > 1, the exchange; returns the full [M, N].
+        chained: the wait for a step's exchange sits in the next step's kernel (where a consumer of the
+        gathered result would have it); the chain is closed by peer_out.wait()."""
         if fused:
-            return sharded_matmul_allgather(layers[i % copies], x, peer_out)
+            return sharded_matmul_allgather(layers[i % copies], x, peer_out, chained=chained)
         q, s, b = weights[i % copies]
         rc = lib.b200q_qmm(P(x), P(q), P(s), P(b), P(y), _lib.BF16, 1, M_DEC, n_loc, K_DEC, GROUP, BITS, 1, 0,
                            P(ws), ws.numel(), sp)
@@ -475,7 +477,9 @@ def main():
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i in range(args.steps):
-                step(i)
+                step(i, chained=True)
+            if fused:
+                peer_out.wait()   # closes the chain: every step's result is complete on every rank
         launches = int(lib.b200q_launch_count() - launches0)
         graph.replay()  # one untimed replay to settle the instantiated graph
         barrier()
@@ -732,7 +736,8 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "arm": "N-sharded over the ranks" + ((", all_gather of outputs per step " + ("fused into the kernel epilogue (peer stores over NVLink, "
-                              "flags raised by the kernel's last thread block, one bounded wait)" if fused else "by NCCL")) if world > 1 else ""),
+                              "flags raised by the kernel's last thread block; every kernel waits for the previous step's flags of all ranks "
+                              "before it reads x or stores y, one bounded wait closes the chain)" if fused else "by NCCL")) if world > 1 else ""),
                        "l2": f"weights rotated over {copies} distinct copies ({copies * shard_bytes / 1e6:.0f} MB per rank, "
                              f"more than twice the {L2_BYTES / 1e6:.0f} MB L2) so every step reads HBM",
                        "weights": "declared constant (b200q_set_weights_constant): requested before the previous kernel has finished",

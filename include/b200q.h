@@ -268,13 +268,21 @@ int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uin
  * counter_local is one more device word of this rank (starts at zero, left at zero) that counts
  * finished thread blocks.  Where the selected kernel has no such epilogue (the register-path
  * decode kernel for 3-, 5- and 6-bit weights) the signal is launched separately, as before.
+ * wait_flag_local (b200q_qmm_sharded_signal only; may be NULL) moves the wait to the consumer:
+ * when given (this rank's own flag), the call does not read x nor store y before the flag has
+ * reached the epoch the previous step left, i.e. before every rank has finished the previous
+ * exchange step - what a kernel needs whose x is the gathered output of that step.  The decode
+ * kernel waits inside (its weight stream starts meanwhile, so a chain of sharded layers costs
+ * one launch per layer); in front of the other kernels the wait is launched on its own.  The
+ * last step of a chain still needs b200q_peer_wait before its result is used.  Same bound and
+ * status code as b200q_peer_wait.
  * The exchange these replace: AllGather::eval_gpu (mlx/backend/cuda/distributed.cu:57-83).
  */
 int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                              void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
                              int64_t M, int64_t N_local, int64_t K, int group_size, int bits,
                              uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                             void* ws, size_t ws_bytes, void* stream);
+                             const uint32_t* wait_flag_local, void* ws, size_t ws_bytes, void* stream);
 int b200q_gather_qmm_sharded_signal(const void* x, const uint32_t* wq_local, const void* scales_local,
                                     const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
                                     int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,

@@ -21,6 +21,11 @@ struct PeerSignal {
   uint32_t* epoch;
   uint32_t* counter;
   int n;   // 0: no signal
+  // Consumer-side wait: when set, the kernel does not read x or store y before this rank's flag
+  // has reached the epoch as the previous kernel of the stream left it, i.e. before every rank
+  // has finished the previous exchange step (bounded by wait_limit SM cycles, then status 6).
+  const uint32_t* wait_flag;
+  long long wait_limit;
 };
 struct PeerOut {
   void* y[kMaxPeers];
@@ -30,6 +35,23 @@ struct PeerOut {
 };
 
 #ifdef __CUDACC__
+// Called by one lane of every warp that is about to touch what the previous exchange step's
+// consumers may still be using.  Returns false when the bound ran out (status word set).
+__device__ __forceinline__ bool peer_wait_previous(const PeerSignal& ps, uint32_t* status) {
+  if (ps.wait_flag == nullptr) return true;
+  const uint32_t expected = *reinterpret_cast<const volatile uint32_t*>(ps.epoch);
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ps.wait_flag) : "memory");
+    if ((int32_t)(v - expected) >= 0) return true;
+    if (clock64() - t0 > ps.wait_limit) {
+      if (status) { atomicMax(&status[0], 6u); status[1] = v; }
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
 // Called by ONE thread of every thread block after all peer stores of the block have been issued
 // and ordered before this thread (a block- or warp-wide barrier).
 __device__ __forceinline__ void peer_signal_tail(const PeerSignal& ps) {

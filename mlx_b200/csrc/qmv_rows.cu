@@ -337,6 +337,8 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // partial buffer, and stores y (or keeps running sums while K is walked in phases).
       asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
       asm volatile("griddepcontrol.wait;" ::: "memory");   // y may still be in use by the previous kernel
+      if (lane == 0) peer_wait_previous(p.sig, p.status);  // ... or by a peer's consumer of the step before
+      __syncwarp();
       int rph = 0, rrg = 0, rslot = 0, ruse = 0;
       for (int red = 0; red < total; ++red) {
         if (!mbar_wait(done0 + 8 * rslot, ruse & 1, abort_flag)) break;
@@ -428,6 +430,10 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   // ================================= consumer warps ===========================================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsConsumer));
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (p.sig.wait_flag != nullptr) {   // x is the gathered output of the previous exchange step
+    if (lane == 0) peer_wait_previous(p.sig, p.status);
+    __syncwarp();
+  }
   RP_MARK(2);
   uint32_t X[UW][MT][NP];         // B fragments of this warp's K slice, pre-scaled
   uint32_t sx_hi[MT], sx_lo[MT];  // scaled group sums of x for groups 2t, 2t+1 of the slice (bf16 hi / lo parts)

@@ -190,6 +190,15 @@ class PeerOutput:
         """This rank's copy of the gathered [m, n_total] result in buffer `buf`."""
         return self._views[buf][:m]
 
+    def wait(self) -> None:
+        """Makes the current stream wait (bounded) until every rank's part of the last exchange step
+        has landed in this rank's buffer."""
+        if self._ws is None:
+            return
+        status = ctypes.c_void_p(self._ws.data_ptr() + self._ws.numel() - 16)
+        st = ctypes.c_void_p(torch.cuda.current_stream(self._ws.device).cuda_stream)
+        _lib.check(self.lib.b200q_peer_wait(ctypes.c_void_p(self.flag[self.rank]), ctypes.c_void_p(self.epoch), status, st))
+
     def check(self) -> None:
         """Synchronises the current stream and raises ops.DeviceStatusError if the last exchange
         did not complete (a peer lagged behind the bounded wait, code 6) or a kernel gave up on one
@@ -210,10 +219,16 @@ class PeerOutput:
         self._own = None
 
 
-def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tensor, out: PeerOutput) -> torch.Tensor:
+def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tensor, out: PeerOutput,
+                             chained: bool = False) -> torch.Tensor:
     """y = x @ dequant(W)^T for the full W, every rank holding only its rows: one matmul launch
     whose epilogue stores to all ranks and whose last thread block updates the flags, and one
-    bounded wait (`out.check()` tells whether it ran out).  x: [M, K] bf16 CUDA,
+    bounded wait (`out.check()` tells whether it ran out).
+
+    chained=True is for a chain of sharded layers on one stream: the call waits, before it reads x
+    or stores its result, until every rank has finished the PREVIOUS call's exchange (inside the
+    decode kernel, whose weight stream starts meanwhile) and does not wait for its own; the caller
+    ends the chain with `out.wait()` before the last result is used.  x: [M, K] bf16 CUDA,
     the same on every rank.  Returns this rank's [M, N] view (valid until the buffer is used again
     two calls later)."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
@@ -232,11 +247,13 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
     _lib.check(lib.b200q_qmm_sharded_signal(vp(x), vp(layer.weight), vp(layer.scales), vp(layer.biases), out.y_ptrs(buf),
                                             out.world, out.n_total, out.rank * layer.n_local, dt, M, layer.n_local, K,
                                             layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
-                                            ctypes.c_void_p(out.counter), vp(ws), ws.numel(), st))
+                                            ctypes.c_void_p(out.counter),
+                                            ctypes.c_void_p(out.flag[out.rank] if (chained and out.step > 0) else 0),
+                                            vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
-    status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
-    _lib.check(lib.b200q_peer_wait(ctypes.c_void_p(out.flag[out.rank]), ctypes.c_void_p(out.epoch), status, st))
+    if not chained:
+        out.wait()
     return out.local(buf, M)
 
 
@@ -350,7 +367,7 @@ def sharded_matmul_allreduce(layer: QuantizedShardedToAllLinear, x: torch.Tensor
     ys = (ctypes.c_void_p * R)(*[b + buf * out.buf_bytes + out.rank * slot_bytes for b in out.base])
     _lib.check(lib.b200q_qmm_sharded_signal(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M,
                                             N, K, layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
-                                            ctypes.c_void_p(out.counter), vp(ws), ws.numel(), st))
+                                            ctypes.c_void_p(out.counter), ctypes.c_void_p(0), vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
