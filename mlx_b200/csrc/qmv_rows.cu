@@ -865,7 +865,24 @@ bool weights_constant() {
 }
 void set_weights_constant(int on) { g_weights_constant = on ? 1 : 0; }
 
+// 17 to 32 token rows run as two passes of up to 16 rows each: the second pass finds the matrix
+// in L2 when it fits, and both passes together stay below the tensor-memory kernel's cost of
+// unpacking a 128-row tile.  Sharded output (peer buffers, completion signal) stays single-pass.
+static bool two_pass(const QmmArgs& a) { return a.M > 16 && a.M <= 32 && a.peers.n == 0; }
+
+static QmmArgs pass_args(const QmmArgs& a, int64_t row0, int64_t rows) {
+  QmmArgs h = a;
+  h.M = rows;
+  h.x = static_cast<const char*>(a.x) + (size_t)row0 * a.K * 2;
+  h.y = static_cast<char*>(a.y) + (size_t)row0 * a.N * 2;
+  return h;
+}
+
 bool qmv_rows_supported(const QmmArgs& a) {
+  if (two_pass(a)) {
+    if ((a.K * 2) % 16 != 0 || (a.N * 2 * 16) % 16 != 0) return false;
+    return qmv_rows_supported(pass_args(a, 0, 16)) && qmv_rows_supported(pass_args(a, 16, a.M - 16));
+  }
   const uintptr_t al = reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.wq) |
                        reinterpret_cast<uintptr_t>(a.scales) | reinterpret_cast<uintptr_t>(a.biases);
   if (al & 15) return false;
@@ -873,6 +890,10 @@ bool qmv_rows_supported(const QmmArgs& a) {
 }
 
 int qmv_rows(const QmmArgs& a, cudaStream_t st) {
+  if (two_pass(a)) {
+    const int rc = qmv_rows(pass_args(a, 0, 16), st);
+    return rc != B200Q_OK ? rc : qmv_rows(pass_args(a, 16, a.M - 16), st);
+  }
   RowsPlan pl = make_plan(a);
   if (!pl.ok) return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul] qmv_rows: unsupported problem");
   pl.prm.early = weights_constant() ? 1 : 0;

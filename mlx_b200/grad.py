@@ -61,40 +61,55 @@ def jvp(x_tangent: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: 
 
 
 class _GatherQmmFn(torch.autograd.Function):
-    """GatherQMM::vjp wrt x (mlx/primitives.cpp:3718-3772): the cotangent goes through gather_qmm with
-    the transposition flipped and the same rhs_indices, then its rows are added into x at lhs_indices."""
+    """GatherQMM::vjp (mlx/primitives.cpp:3718-3837).  d x: the cotangent goes through gather_qmm with
+    the transposition flipped and the same rhs_indices, then its rows are added into x at lhs_indices.
+    d scales / d biases: the per-pair dense products cotangent_i^T x[lhs_i] (or x[lhs_i]^T cotangent_i)
+    are added into the matrix of the expert rhs_i names (the reference's gather_mm_grad), then summed
+    over each group exactly as in the dense case."""
 
     @staticmethod
     def forward(ctx, x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits):
-        ctx.save_for_backward(w, scales, biases, lhs_indices, rhs_indices)
+        ctx.save_for_backward(w, scales, biases, lhs_indices, rhs_indices, x)
         ctx.cfg = (bool(transpose), group_size, bits, tuple(x.shape), x.dtype)
         return ops.gather_qmm(x, w, scales, biases, lhs_indices, rhs_indices, transpose, group_size, bits)
 
     @staticmethod
     def backward(ctx, cotangent):
-        w, scales, biases, lhs_indices, rhs_indices = ctx.saved_tensors
+        w, scales, biases, lhs_indices, rhs_indices, x = ctx.saved_tensors
         transpose, group_size, bits, x_shape, x_dtype = ctx.cfg
-        if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
-            raise NotImplementedError("[gather_qmm] gradients wrt scales and biases are not provided")
-        if not ctx.needs_input_grad[0]:
-            return (None,) * 9
         idx_shape = tuple(cotangent.shape[:-2])
         M = cotangent.shape[-2]
         rhs = torch.broadcast_to(rhs_indices, idx_shape).reshape(-1)
         lhs = torch.broadcast_to(lhs_indices, idx_shape).reshape(-1).to(torch.int64)
-        g = ops.gather_qmm(cotangent.reshape((-1, M, cotangent.shape[-1])).contiguous(), w, scales, biases, None, rhs,
-                           not transpose, group_size, bits)          # [n_idx, M, K]
-        dx = torch.zeros((max(1, torch.Size(x_shape[:-2]).numel()),) + tuple(x_shape[-2:]), dtype=torch.float32,
-                         device=g.device)
-        dx.index_add_(0, lhs, g.float())
-        return (dx.to(x_dtype).reshape(x_shape),) + (None,) * 8
+        fc = cotangent.reshape((-1, M, cotangent.shape[-1])).contiguous()
+        dx = ds = db = None
+        if ctx.needs_input_grad[0]:
+            g = ops.gather_qmm(fc, w, scales, biases, None, rhs, not transpose, group_size, bits)   # [n_idx, M, K]
+            dx = torch.zeros((max(1, torch.Size(x_shape[:-2]).numel()),) + tuple(x_shape[-2:]), dtype=torch.float32,
+                             device=g.device)
+            dx.index_add_(0, lhs, g.float())
+            dx = dx.to(x_dtype).reshape(x_shape)
+        if ctx.needs_input_grad[2] or ctx.needs_input_grad[3]:
+            xs = x.reshape((-1,) + tuple(x_shape[-2:]))[lhs].float()                # [n_idx, M, K]
+            cf = fc.float()
+            pair = cf.transpose(1, 2) @ xs if transpose else xs.transpose(1, 2) @ cf
+            n_mat = max(1, torch.Size(w.shape[:-2]).numel())
+            dw = torch.zeros((n_mat,) + tuple(pair.shape[-2:]), dtype=torch.float32, device=pair.device)
+            dw.index_add_(0, rhs.to(torch.int64), pair)
+            dsb = dw.reshape(tuple(w.shape[:-2]) + tuple(pair.shape[-2:])).unflatten(-1, (-1, group_size))
+            if ctx.needs_input_grad[3]:
+                db = dsb.sum(-1).to(biases.dtype)
+            if ctx.needs_input_grad[2]:
+                q = ops.dequantize(w, torch.ones_like(scales), torch.zeros_like(biases), group_size, bits)
+                ds = (dsb * q.unflatten(-1, (-1, group_size)).float()).sum(-1).to(scales.dtype)
+        return dx, None, ds, db, None, None, None, None, None
 
 
 def gather_qmm(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
                lhs_indices: Optional[torch.Tensor] = None, rhs_indices: Optional[torch.Tensor] = None,
                transpose: bool = True, group_size: Optional[int] = None, bits: Optional[int] = None,
                mode: str = "affine") -> torch.Tensor:
-    """ops.gather_qmm with autograd support for x."""
+    """ops.gather_qmm with autograd support for x, scales and biases."""
     group_size, bits = ops._mode_params(mode, group_size, bits, "gather_qmm")
     if lhs_indices is None and rhs_indices is None:
         return quantized_matmul(x, w, scales, biases, transpose, group_size, bits)

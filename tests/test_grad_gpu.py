@@ -71,16 +71,23 @@ def test_gather_qmm_vjp_matches_dense_autograd(transpose):
     w = torch.randn((E, N, K) if transpose else (E, K, N), device="cuda")
     wq, s, b = mb.quantize(w, g, bits)
     x = torch.randn(B, M, K, device="cuda", requires_grad=True)
+    s.requires_grad_(True)
+    b.requires_grad_(True)
     lhs = torch.tensor([0, 0, 3, 5, 5, 5, 2], device="cuda")
-    rhs = torch.tensor([1, 3, 0, 2, 2, 1, 3], device="cuda")
+    rhs = torch.tensor([1, 3, 0, 1, 1, 1, 3], device="cuda")        # expert 2 is never used
     y = grad.gather_qmm(x, wq, s, b, lhs, rhs, transpose, g, bits)
     assert tuple(y.shape) == (7, M, N)
     c = torch.randn_like(y)
-    (dx,) = torch.autograd.grad(y, (x,), c)
-    wd = mb.dequantize(wq, s, b, g, bits).double()
-    x64 = x.detach().double().requires_grad_(True)
+    dx, ds, db = torch.autograd.grad(y, (x, s, b), c)
+    q = mb.dequantize(wq, torch.ones_like(s), torch.zeros_like(b), g, bits).double()
+    x64, s64, b64 = (t.detach().double().requires_grad_(True) for t in (x, s, b))
+    wd = (q.unflatten(-1, (-1, g)) * s64.unsqueeze(-1) + b64.unsqueeze(-1)).flatten(-2)
     y64 = torch.stack([x64[l] @ (wd[r].transpose(0, 1) if transpose else wd[r]) for l, r in zip(lhs.tolist(), rhs.tolist())])
-    (rx,) = torch.autograd.grad(y64, (x64,), c.double())
+    rx, rs, rb = torch.autograd.grad(y64, (x64, s64, b64), c.double())
     assert float((y.detach().double() - y64.detach()).abs().max()) <= 1e-3 * float(y64.detach().abs().max())
     assert dx.shape == x.shape and float((dx.double() - rx).abs().max()) <= 1e-3 * float(rx.abs().max())
     assert not dx[1].any() and not dx[4].any()       # rows no index pair reads get no gradient
+    # d scales / d biases (mlx/primitives.cpp:3780-3834): fp32 sums, TF32 allowed in the dense products
+    for got, ref in ((ds, rs), (db, rb)):
+        assert got.shape == ref.shape and float((got.double() - ref).abs().max()) <= 2e-3 * float(ref.abs().max())
+    assert not ds[2].any() and not db[2].any()       # an expert no pair names gets no gradient

@@ -190,8 +190,23 @@ def test_row_owning_kernel_long_k_phases(M, N, K, bits, g):
     run_case("bf16", M, N, K, g, bits, seed=M + K, expect_kernel=("qmv_rows",))
 
 
+@pytest.mark.parametrize("M,N,K,bits,g", [(17, 2504, 4096, 4, 64), (24, 1024, 2048, 8, 32), (25, 520, 8192, 2, 64),
+                                          (32, 14336, 4096, 4, 64)])
+def test_row_owning_kernel_two_passes(M, N, K, bits, g):
+    """17 to 32 token rows: two passes of the row-owning kernel (16 rows, then the rest)."""
+    run_case("bf16", M, N, K, g, bits, seed=M + N, expect_kernel=("qmv_rows",))
+
+
+def test_kernel_selection_by_token_count():
+    """The selection a caller sees for C2's matrix as the token count grows."""
+    name = lambda M, **kw: mb.qmm_kernel_name(torch.bfloat16, M, 14336, 4096, kw.get("g", 64), kw.get("bits", 4))
+    assert [name(M) for M in (1, 16, 17, 32, 33, 64, 512)] == ["qmv_rows"] * 4 + ["qmm_tcgen05"] * 3
+    assert name(32, bits=3) == "qmm_tcgen05" and name(16, bits=3) == "qmv_mma"
+
+
 def test_row_owning_kernel_extreme_activations():
-    """x is pre-scaled by 2^64 inside the kernel: values up to 2^60 and down to 2^-60 must survive."""
+    """Each warp scales its x slice by a power of two chosen from the slice's magnitude: values
+    up to 2^60 and down to 2^-60 must survive."""
     dtype, M, N, K = "bf16", 4, 256, 1024
     w = make_w(7, (N, K), dtype)
     wq, s, b = O.quantize(w, 64, 4, dtype)
