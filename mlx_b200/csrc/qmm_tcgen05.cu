@@ -9,8 +9,10 @@
 // to 256 tokens per instruction, and the operand that streams unchanged (x) is B.
 //
 //   thread A: TMA  --packed W tile [128 rows x 128 k, 16*bits bytes per row]-->  smem ring P
-//   8 dequant warps: one thread per weight row (= one TMEM lane): unpack 32 k with
-//        shift/lop3/prmt, apply s*q+b in bf16x2, tcgen05.st into the A ring in TMEM
+//   16 dequant warps in two sets of 8 (even / odd 64-k blocks): one thread per weight row
+//        (= one TMEM lane): unpack 32 k with shift/lop3/prmt, apply s*q+b in bf16x2,
+//        tcgen05.st into the A ring in TMEM.  The unpack of one block is a chain of
+//        dependent ALU work; four dequant warps per SM sub-partition keep its pipes busy
 //   thread B: TMA  --x tile [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
 //   1 thread: tcgen05.mma.kind::f16 (A from TMEM, B from smem descriptors), fp32
 //        accumulator [128 lanes x NT columns] in TMEM, tcgen05.commit on mbarriers
@@ -42,21 +44,35 @@ namespace b200q {
 namespace {
 
 constexpr int kTileN = 128;       // weight rows per tile (MMA M)
-constexpr int kBlockK = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
-constexpr int kStagesA = 8;       // A ring in TMEM (32 columns each)
-constexpr int kMaxStagesB = 6;
-// x tiles in shared memory.  Six stages fit next to the packed ring for bits <= 4 but measured
-// slower (474 us against 443 us on M=4096, N=14336, K=4096): four it is.
-__host__ __device__ constexpr int stages_b(int) { return 4; }
-constexpr int kStagesP = 4;       // packed W tiles in shared memory
+constexpr int kBlockK = 64;       // k per x sub-tile (one 128-byte swizzle row of bf16)
+constexpr int kStageK = 128;      // k per pipeline stage: two x sub-tiles, one packed tile, 8 MMAs
+constexpr int kStagesA = 4;       // A ring in TMEM (64 columns each)
+constexpr int kMaxStagesB = 6;    // x stages in shared memory: as many as fit (3 at 256 tokens)
+constexpr int kMaxStagesP = 4;    // packed W tiles in shared memory
+// Packed stages: 16 * bits bytes per row and stage; next to three 64 KB x stages 35 KB remain.
+__host__ __device__ constexpr int stages_p(int bits) { return bits <= 4 ? 4 : (bits == 5 ? 3 : 2); }
+constexpr size_t kSmemMax = 227 * 1024;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 16;   // 4 TMEM lane quadrants x 4 quarters (32 k) of a stage
 constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each drains half of the columns
 constexpr int kProducerPWarp = 2 + kDequantWarps + kEpilogueWarps;  // last warp
-constexpr int kThreads = 32 * (3 + kDequantWarps + kEpilogueWarps);  // 608
+constexpr int kThreads = 32 * (3 + kDequantWarps + kEpilogueWarps);  // 864
 
 using namespace tc;
+
+// Waits of the three single-thread roles.
+#ifndef B200Q_TC_PARK
+#define TC_WAIT1 mbar_wait_spin
+#else
+#define TC_WAIT1 mbar_wait
+#endif
+// Waits of the dequant warps.
+#ifdef B200Q_TC_DQ_SPIN
+#define TC_WAIT16 mbar_wait_spin
+#else
+#define TC_WAIT16 mbar_wait
+#endif
 
 // Shared-memory matrix descriptor of a K-major, 128-byte-swizzled operand tile whose
 // rows are 128 bytes (64 bf16): 8-row groups are 1024 bytes apart (SBO), descriptor
@@ -100,12 +116,13 @@ struct TcParams {
   uint32_t* status;
   int M, N, K;
   int NT;            // tokens per tile (multiple of 16, <= 256)
+  int nsb;           // x stages in shared memory (2 .. kMaxStagesB)
   int n_tiles, m_tiles;
   int group_shift;   // log2(group / 32)
 };
 
 struct __align__(8) Barriers {
-  uint64_t full_p[kStagesP], empty_p[kStagesP];
+  uint64_t full_p[kMaxStagesP], empty_p[kMaxStagesP];
   uint64_t full_b[kMaxStagesB], empty_b[kMaxStagesB];
   uint64_t full_a[kStagesA], empty_a[kStagesA];
   uint64_t acc_full, acc_empty;
@@ -121,7 +138,33 @@ __device__ __forceinline__ void dequant32(const uint32_t (&w)[BITS], uint32_t s_
                                           uint32_t (&out)[16]) {
   constexpr uint32_t kMagic = 0x43004300u;  // (128.0, 128.0): 0x4300 | q == 128 + q for q < 128
   const uint32_t s2 = s_bits * 0x00010001u, b2 = b_bits * 0x00010001u;
+  // Fast form for 4- and 8-bit fields: the masked field, read as bf16, is the subnormal (or
+  // smallest normal) number q * 2^-133 (16 q * 2^-133 for a field at bits 4..7: bit 7 is the
+  // exponent's lowest bit and continues the subnormal scale exactly).  fma.rn.bf16x2 takes
+  // subnormal inputs exactly, so one fma with the scale times 2^133 (2^129) gives
+  // round(q * s + b): no shift for half of the fields, no subtraction.  It needs the scaled scale
+  // to stay finite and normal: biased exponent of s in [1, 121]; other scales (zero, subnormal,
+  // |s| >= 2^-6 * 2, inf, nan) take the general form below.
+  const uint32_t s_exp = (s_bits >> 7) & 0xFFu;
+  const bool fast = s_exp >= 1u && s_exp <= 121u;
   if constexpr (BITS == 4) {
+    if (fast) {
+      const uint32_t sl = (s_bits + (133u << 7)) * 0x00010001u, sh = (s_bits + (129u << 7)) * 0x00010001u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t u = w[j] >> 8;
+        uint32_t p[4];   // p[i] = (w[i], w[i+4]) as bf16 pairs
+        p[0] = fma_bf16x2(w[j] & 0x000F000Fu, sl, b2);
+        p[1] = fma_bf16x2(w[j] & 0x00F000F0u, sh, b2);
+        p[2] = fma_bf16x2(u & 0x000F000Fu, sl, b2);
+        p[3] = fma_bf16x2(u & 0x00F000F0u, sh, b2);
+        out[4 * j + 0] = __byte_perm(p[0], p[1], 0x5410);
+        out[4 * j + 1] = __byte_perm(p[2], p[3], 0x5410);
+        out[4 * j + 2] = __byte_perm(p[0], p[1], 0x7632);
+        out[4 * j + 3] = __byte_perm(p[2], p[3], 0x7632);
+      }
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint32_t p[4];
@@ -137,6 +180,17 @@ __device__ __forceinline__ void dequant32(const uint32_t (&w)[BITS], uint32_t s_
       out[4 * j + 3] = __byte_perm(p[2], p[3], 0x7632);  // (w6, w7)
     }
   } else if constexpr (BITS == 8) {
+    if (fast) {
+      const uint32_t sl = (s_bits + (133u << 7)) * 0x00010001u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t r0 = fma_bf16x2(w[j] & 0x00FF00FFu, sl, b2);          // (w0, w2)
+        const uint32_t r1 = fma_bf16x2((w[j] >> 8) & 0x00FF00FFu, sl, b2);   // (w1, w3)
+        out[2 * j + 0] = __byte_perm(r0, r1, 0x5410);
+        out[2 * j + 1] = __byte_perm(r0, r1, 0x7632);
+      }
+      return;
+    }
     // 8-bit values exceed the bf16 integer trick: go through float (0x4B0000qq == 2^23 + q)
     const float sf = __uint_as_float(s_bits << 16), bf = __uint_as_float(b_bits << 16);
 #pragma unroll
@@ -202,16 +256,17 @@ template <int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const TcParams p) {
-  // A packed stage holds 128 k of every row (16*BITS bytes, a multiple of 16 for every width)
-  // and feeds two 64-k MMA blocks.
+  // A packed stage holds 128 k of every row (16*BITS bytes, a multiple of 16 for every width).
   constexpr int kPRowBytes = 16 * BITS;
-  constexpr int kStagesB = stages_b(BITS);
+  constexpr int kStagesP = stages_p(BITS);
   constexpr int kPStageBytes = kTileN * kPRowBytes;
+  const int kStagesB = p.nsb;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // carve-up: [B ring: kStagesB * NT*128 B (1024-aligned)] [P ring: kStagesP * 4096 B] [barriers]
+  // carve-up: [B ring: nsb stages of two NT*128-byte sub-tiles (1024-aligned)] [P ring] [barriers]
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t b_stage_bytes = (uint32_t)p.NT * 128u;
-  const uint32_t b_stage_pitch = (b_stage_bytes + 1023u) & ~1023u;
+  const uint32_t b_sub_bytes = (uint32_t)p.NT * 128u;     // NT is a multiple of 16: a multiple of 2048
+  const uint32_t b_stage_bytes = 2u * b_sub_bytes;
+  const uint32_t b_stage_pitch = b_stage_bytes;
   unsigned char* ring_b = smem;
   unsigned char* ring_p = ring_b + (size_t)kStagesB * b_stage_pitch;
   Barriers* bars = reinterpret_cast<Barriers*>(ring_p + (size_t)kStagesP * kPStageBytes);
@@ -222,7 +277,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   // Tuning builds (plain mode only): thread block 0 leaves per-role wait cycles / 16 in a buffer of
   // its own (g_tc_prof), which a test harness reads back with cudaMemcpyFromSymbol.
   uint32_t* dbg = g_tc_prof;
-  long long pw0 = 0, pw1 = 0, pw2 = 0, pt = 0;
+  long long pw0 = 0, pw1 = 0, pw2 = 0, pw3 = 0, pw4 = 0, pt = 0;
   const long long prof_entry = clock64();
 #define TC_T0() pt = clock64()
 #define TC_ACC(v) v += clock64() - pt
@@ -232,7 +287,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 #define TC_ACC(v)
 #define TC_OUT(slot, v)
 #endif
-  const int kblocks = p.K / kBlockK;
+  const int kstages = p.K / kStageK;
   const int total_tiles = p.mtiles ? *p.n_mtiles * p.n_tiles : p.n_tiles * p.m_tiles;
 
   if (threadIdx.x == 0) {
@@ -258,17 +313,20 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: x tiles (B ring)
     if (lane == 0) {
-      uint32_t it = 0;  // k-block counter across tiles
+      uint32_t sb = 0, pb = 0;  // stage and phase, running across tiles
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc_ = tile_coord(p, tile);
         bool ok = true;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
+        for (int ks = 0; ks < kstages; ++ks) {
           TC_T0();
-          if (!mbar_wait(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) { ok = false; break; }
+          if (!TC_WAIT1(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) { ok = false; break; }
           TC_ACC(pw1);
-          mbar_expect_tx(smem_u32(&bars->full_b[sb]), b_stage_bytes);
-          tma_load_2d(smem_u32(ring_b + sb * b_stage_pitch), &map_x, kb * kBlockK, tc_.x_row0, smem_u32(&bars->full_b[sb]));
+          const uint32_t bar = smem_u32(&bars->full_b[sb]);
+          const uint32_t dst = smem_u32(ring_b + sb * b_stage_pitch);
+          mbar_expect_tx(bar, b_stage_bytes);
+          tma_load_2d(dst, &map_x, ks * kStageK, tc_.x_row0, bar);
+          tma_load_2d(dst + b_sub_bytes, &map_x, ks * kStageK + kBlockK, tc_.x_row0, bar);
+          if (++sb == (uint32_t)kStagesB) { sb = 0; pb ^= 1; }
         }
         if (!ok) break;
       }
@@ -279,18 +337,18 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     // A separate thread: behind the x-tile waits of the other producer the packed tiles would
     // arrive late and starve the dequant warps.
     if (lane == 0) {
-      uint32_t itp = 0;  // packed stages advance every second k-block (kblocks is even)
+      uint32_t sp = 0, pp = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc_ = tile_coord(p, tile);
         bool ok = true;
-        for (int kp = 0; kp < kblocks / 2; ++kp, ++itp) {
-          const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
+        for (int ks = 0; ks < kstages; ++ks) {
           TC_T0();
-          if (!mbar_wait(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) { ok = false; break; }
+          if (!TC_WAIT1(smem_u32(&bars->empty_p[sp]), pp ^ 1, abort_flag)) { ok = false; break; }
           TC_ACC(pw0);
           mbar_expect_tx(smem_u32(&bars->full_p[sp]), kPStageBytes);
-          tma_load_2d(smem_u32(ring_p + sp * kPStageBytes), &map_w, kp * kPRowBytes, tc_.w_row0,
+          tma_load_2d(smem_u32(ring_p + sp * kPStageBytes), &map_w, ks * kPRowBytes, tc_.w_row0,
                       smem_u32(&bars->full_p[sp]));
+          if (++sp == (uint32_t)kStagesP) { sp = 0; pp ^= 1; }
         }
         if (!ok) break;
       }
@@ -300,46 +358,53 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(p.NT);
-      uint32_t it = 0, tcount = 0;
+      uint32_t tcount = 0, sa = 0, pa = 0, sb = 0, pb = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
         TC_T0();
-        if (!mbar_wait(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
+        if (!TC_WAIT1(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
         TC_ACC(pw2);
         tcgen05_fence_after();
         bool ok = true;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
-          const uint32_t sb = it % kStagesB, pb = (it / kStagesB) & 1;
+        for (int ks = 0; ks < kstages; ++ks) {
           TC_T0();
-          if (!mbar_wait(smem_u32(&bars->full_a[sa]), pa, abort_flag)) { ok = false; break; }
+          if (!TC_WAIT1(smem_u32(&bars->full_a[sa]), pa, abort_flag)) { ok = false; break; }
           TC_ACC(pw0);
           TC_T0();
-          if (!mbar_wait(smem_u32(&bars->full_b[sb]), pb, abort_flag)) { ok = false; break; }
+          if (!TC_WAIT1(smem_u32(&bars->full_b[sb]), pb, abort_flag)) { ok = false; break; }
           TC_ACC(pw1);
           tcgen05_fence_after();
           const uint32_t b_addr = smem_u32(ring_b + sb * b_stage_pitch);
+          TC_T0();
 #pragma unroll
-          for (int kk = 0; kk < kBlockK / 16; ++kk) {
-            tcgen05_mma_ts(tmem_acc, tmem_a + sa * 32 + kk * 8, make_sw128_desc(b_addr + kk * 32), idesc,
-                           (kb | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < kStageK / 16; ++kk) {
+            tcgen05_mma_ts(tmem_acc, tmem_a + sa * 64 + kk * 8,
+                           make_sw128_desc(b_addr + (kk >> 2) * b_sub_bytes + (kk & 3) * 32), idesc,
+                           (ks | kk) != 0 ? 1u : 0u);
           }
+          TC_ACC(pw3);
+          TC_T0();
+          // one arrival per ring and stage: the issuing thread pays for every commit, so a stage
+          // is 128 k (eight MMAs) deep
           tcgen05_commit(smem_u32(&bars->empty_a[sa]));
           tcgen05_commit(smem_u32(&bars->empty_b[sb]));
+          TC_ACC(pw4);
+          if (++sa == (uint32_t)kStagesA) { sa = 0; pa ^= 1; }
+          if (++sb == (uint32_t)kStagesB) { sb = 0; pb ^= 1; }
         }
         if (!ok) break;
         tcgen05_commit(smem_u32(&bars->acc_full));
       }
-      TC_OUT(4, pw0); TC_OUT(5, pw1); TC_OUT(6, pw2); TC_OUT(7, clock64() - prof_entry);
+      TC_OUT(4, pw0); TC_OUT(5, pw1); TC_OUT(6, pw2); TC_OUT(7, clock64() - prof_entry); TC_OUT(14, pw3); TC_OUT(15, pw4);
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------------------------------------ dequant: one thread per weight row
     const int dq = warp - 2;
     const int quad = warp & 3;           // TMEM lane quadrant this warp may access
-    const int half = dq >> 2;            // which 32-k half of the 64-k block
+    const int kq = dq >> 2;              // which 32-k quarter of the 128-k stage
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     const int row_groups = p.K >> (5 + p.group_shift);
-    uint32_t it = 0;
+    uint32_t sa = 0, pa = 0, sp = 0, pp = 0;
     // The arrival for an A stage is deferred until the next stage has been unpacked, so the
     // latency of the tensor-memory store overlaps the next block's ALU work.
     bool pending = false;
@@ -351,33 +416,64 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[pending_sa]));
       pending = false;
     };
+    // Scales and biases: a thread needs one 2-byte value of each per stage, from a row of its own,
+    // so a warp's load touches 32 cache lines whatever its width.  Fetched per stage they kept the
+    // load/store pipe busier than anything else in the kernel; fetched as 16-byte chunks (eight
+    // groups of the row) there are up to eight times fewer loads.  `cur` holds the chunk in use,
+    // `nxt` the next one of the sequence (tile by tile, chunk by chunk), requested one chunk early.
+    const int gs5 = 5 + p.group_shift;
+    const bool vec = (row_groups & 7) == 0 && ((reinterpret_cast<uintptr_t>(p.scales) | reinterpret_cast<uintptr_t>(p.biases)) & 15) == 0;
+    const int nchunks = row_groups >> 3;
+    uint4 s_cur4 = make_uint4(0, 0, 0, 0), b_cur4 = s_cur4, s_nxt4 = s_cur4, b_nxt4 = s_cur4;
+    int pf_tile = blockIdx.x, pf_chunk = 0;   // next chunk to request
+    auto row_of = [&](int tile_) {
+      const TileCoord t_ = tile_coord(p, tile_);
+      const int r_ = t_.w_row0 + row_in_tile;
+      return r_ < t_.w_rows_end ? r_ : t_.w_rows_end - 1;   // rows past N: results are never stored
+    };
+    auto prefetch = [&]() {
+      if (pf_tile >= total_tiles) return;
+      const size_t off = (size_t)row_of(pf_tile) * row_groups + (size_t)pf_chunk * 8;
+      s_nxt4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.scales) + off));
+      b_nxt4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.biases) + off));
+      if (++pf_chunk == nchunks) { pf_chunk = 0; pf_tile += gridDim.x; }
+    };
+    auto pick = [](const uint4& c, int idx) {
+      const uint32_t wsel = idx < 4 ? (idx < 2 ? c.x : c.y) : (idx < 6 ? c.z : c.w);
+      return (idx & 1) ? (wsel >> 16) : (wsel & 0xFFFFu);
+    };
+    if (vec) prefetch();
+    int cur_chunk = -1;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-      const TileCoord tc_ = tile_coord(p, tile);
-      int row = tc_.w_row0 + row_in_tile;
-      row = row < tc_.w_rows_end ? row : tc_.w_rows_end - 1;  // rows past N: results are never stored
+      const int row = row_of(tile);
       const unsigned short* sc = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * row_groups;
       const unsigned short* bi = reinterpret_cast<const unsigned short*>(p.biases) + (size_t)row * row_groups;
-      uint32_t s_next = __ldg(sc + ((half * 32) >> (5 + p.group_shift)));
-      uint32_t b_next = __ldg(bi + ((half * 32) >> (5 + p.group_shift)));
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const uint32_t itp = it >> 1;
-        const uint32_t sp = itp % kStagesP, pp = (itp / kStagesP) & 1;
-        const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1;
-        const uint32_t s_cur = s_next, b_cur = b_next;
-        if (kb + 1 < kblocks) {
-          const int g = ((kb + 1) * kBlockK + half * 32) >> (5 + p.group_shift);
-          s_next = __ldg(sc + g);
-          b_next = __ldg(bi + g);
+      uint32_t s_next = 0, b_next = 0;
+      if (!vec) {
+        s_next = __ldg(sc + ((kq * 32) >> gs5));
+        b_next = __ldg(bi + ((kq * 32) >> gs5));
+      }
+      cur_chunk = -1;
+      for (int ks = 0; ks < kstages; ++ks) {
+        uint32_t s_cur = s_next, b_cur = b_next;
+        if (vec) {
+          const int g = (ks * kStageK + kq * 32) >> gs5;
+          if ((g >> 3) != cur_chunk) {
+            s_cur4 = s_nxt4; b_cur4 = b_nxt4;
+            cur_chunk = g >> 3;
+            prefetch();
+          }
+          s_cur = pick(s_cur4, g & 7);
+          b_cur = pick(b_cur4, g & 7);
         }
         TC_T0();
-        if ((it & 1) == 0 && !mbar_wait(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
+        if (!TC_WAIT16(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
         TC_ACC(pw0);
-        // this thread's 32 fields: BITS words at (64-k block parity, 32-k half) of its row
+        // this thread's 32 fields: BITS words at quarter kq of its row
         uint32_t w[BITS];
         {
-          const unsigned char* src = ring_p + sp * kPStageBytes + row_in_tile * kPRowBytes +
-                                     ((it & 1) * 2 + half) * (4 * BITS);
+          const unsigned char* src = ring_p + sp * kPStageBytes + row_in_tile * kPRowBytes + kq * (4 * BITS);
           if constexpr (BITS == 4) {
             const uint4 v = *reinterpret_cast<const uint4*>(src);
             w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
@@ -396,28 +492,44 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           }
         }
         uint32_t vals[16];
+        TC_T0();
         dequant32<BITS>(w, s_cur, b_cur, vals);
+#ifdef B200Q_PROFILE
+        asm volatile("" ::"r"(vals[0]), "r"(vals[5]), "r"(vals[10]), "r"(vals[15]));
+#endif
+        TC_ACC(pw3);
+        // (scalar form, rows whose group count is not a multiple of eight) the next stage's scale
+        // and bias are requested after the unpack
+        if (!vec && ks + 1 < kstages) {
+          const int g = ((ks + 1) * kStageK + kq * 32) >> gs5;
+          s_next = __ldg(sc + g);
+          b_next = __ldg(bi + g);
+        }
         TC_T0();
         if (pending) publish();
         TC_ACC(pw1);
         TC_T0();
-        if (!mbar_wait(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
+        if (!TC_WAIT16(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
         TC_ACC(pw2);
         tcgen05_fence_after();
-        tcgen05_st_x16(tmem_a + lane_field + sa * 32 + half * 16, vals);
+        TC_T0();
+        tcgen05_st_x16(tmem_a + lane_field + sa * 64 + kq * 16, vals);
+        TC_ACC(pw4);
         pending = true;
         pending_sa = sa;
         // The packed stage is released only here, after the store that consumes the unpacked
         // registers has been issued: the shared-memory reads above have then returned for every
         // lane, so the refill of the stage cannot overtake them.
-        if (it & 1) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
+        if (++sa == (uint32_t)kStagesA) { sa = 0; pa ^= 1; }
+        if (++sp == (uint32_t)kStagesP) { sp = 0; pp ^= 1; }
       }
     }
     if (pending) publish();
     if (warp == 2) { TC_OUT(8, pw0); TC_OUT(9, pw1); TC_OUT(10, pw2); TC_OUT(11, clock64() - prof_entry); }
+    TC_OUT(16 + dq, pw2); TC_OUT(32 + dq, pw0);
+    if (warp == 2) { TC_OUT(48, pw3); TC_OUT(49, pw4); }
   } else if (warp < kProducerPWarp) {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;
@@ -502,9 +614,16 @@ int pick_nt(int64_t M) {
   return (int)(nt > 256 ? 256 : nt);
 }
 
+// x stages that fit next to the packed ring (each holds 128 k of nt tokens).
+int x_stages(int nt, int bits) {
+  const size_t fixed = 1024 + (size_t)stages_p(bits) * kTileN * 16 * bits + sizeof(Barriers) + 64;
+  const size_t n = (kSmemMax - fixed) / ((size_t)nt * 256);
+  return (int)(n > (size_t)kMaxStagesB ? (size_t)kMaxStagesB : n);
+}
+
 size_t smem_bytes(int nt, int bits) {
-  const size_t b_pitch = ((size_t)nt * 128 + 1023) & ~size_t(1023);
-  const size_t need = 1024 + stages_b(bits) * b_pitch + (size_t)kStagesP * kTileN * 16 * bits + sizeof(Barriers) + 64;
+  const size_t need = 1024 + (size_t)x_stages(nt, bits) * nt * 256 + (size_t)stages_p(bits) * kTileN * 16 * bits +
+                      sizeof(Barriers) + 64;
   // More than half of an SM's shared memory: guarantees one CTA per SM, so the 512-column
   // tensor-memory allocation never has to wait for a co-resident CTA of this kernel.
   const size_t one_per_sm = 120 * 1024;
@@ -582,6 +701,7 @@ int qmm_tc(const QmmArgs& a, cudaStream_t st) {
   p.status = reinterpret_cast<uint32_t*>(static_cast<char*>(a.ws) + a.ws_bytes - kStatusBytes);
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.NT = nt;
+  p.nsb = x_stages(nt, (int)a.bits);
   p.n_tiles = (int)((a.N + kTileN - 1) / kTileN);
   p.m_tiles = (int)((a.M + nt - 1) / nt);
   p.group_shift = a.group == 32 ? 0 : (a.group == 64 ? 1 : 2);
@@ -636,6 +756,7 @@ int qmm_tc_grouped(const GroupedArgs& a, cudaStream_t st) {
   p.status = a.status;
   p.M = (int)a.n_rows; p.N = (int)a.N; p.K = (int)a.K;
   p.NT = nt;
+  p.nsb = x_stages(nt, (int)a.bits);
   p.n_tiles = (int)((a.N + kTileN - 1) / kTileN);
   p.m_tiles = 0;
   p.group_shift = a.group == 32 ? 0 : (a.group == 64 ? 1 : 2);
