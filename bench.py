@@ -54,7 +54,7 @@ WORKLOAD = (f"decode quantized_matmul M={M_DEC} N={N_DEC} K={K_DEC} bits={BITS} 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode kernel on the one-GPU
 # workload, from an ncu capture of that kernel (a constant, not measured in this run; with the
 # matrix split over R ranks the per-rank traffic is this divided by R: it is all weight stream)
-TRAFFIC_FROM_PROFILE = {"qmv_rows": 33234688, "qmv_mma": 33494784}
+TRAFFIC_FROM_PROFILE = {"qmv_rows": 33222400, "qmv_mma": 33494784}
 
 
 def algorithmic_bytes(M, N, K, bits=BITS, group=GROUP):
@@ -430,8 +430,9 @@ def main():
 
     def step(i, chained=False):
         """One step: the matmul on this rank's rows and, at N > 1, the exchange; returns the full [M, N].
-        chained: the wait for a step's exchange sits in the next step's kernel (where a consumer of the
-        gathered result would have it); the chain is closed by peer_out.wait()."""
+        chained: the wait for a step's exchange sits in the next step's kernel; the chain is closed by
+        peer_out.wait().  "buffers" (x is a replicated input, as in the workload): only the stores into
+        the exchange buffers wait; True (x would be the previous step's gathered output): the loads wait too."""
         if fused:
             return sharded_matmul_allgather(layers[i % copies], x, peer_out, chained=chained)
         q, s, b = weights[i % copies]
@@ -477,7 +478,7 @@ def main():
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i in range(args.steps):
-                step(i, chained=True)
+                step(i, chained="buffers")
             if fused:
                 peer_out.wait()   # closes the chain: every step's result is complete on every rank
         launches = int(lib.b200q_launch_count() - launches0)
@@ -506,6 +507,25 @@ def main():
     total_bytes = algorithmic_bytes(M_DEC, N_DEC, K_DEC)
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     if fused:
+        peer_out.check()
+    # the same steps as a dependent chain (every kernel also holds its x loads until all ranks have
+    # finished the previous step, as if x were that step's gathered output): reported beside the headline
+    ms_dependent = None
+    if fused:
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            for i in range(args.steps):
+                step(i, chained=True)
+            peer_out.wait()
+        g2.replay()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            f0.record(stream)
+            g2.replay()
+            f1.record(stream)
+        barrier()
+        ms_dependent = max_over_ranks(f0.elapsed_time(f1)) / args.steps
         peer_out.check()
 
     # ---- kernel-only duration for the roofline (same stream, events around kernel launches only)
@@ -736,8 +756,9 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "arm": "N-sharded over the ranks" + ((", all_gather of outputs per step " + ("fused into the kernel epilogue (peer stores over NVLink, "
-                              "flags raised by the kernel's last thread block; every kernel waits for the previous step's flags of all ranks "
-                              "before it reads x or stores y, one bounded wait closes the chain)" if fused else "by NCCL")) if world > 1 else ""),
+                              "flags raised by the kernel's last thread block; x is a replicated input, so every kernel holds only its "
+                              "stores into the exchange buffers until all ranks have finished the previous step, one bounded wait closes "
+                              "the chain; ms_per_step_dependent_chain holds the loads back as well)" if fused else "by NCCL")) if world > 1 else ""),
                        "l2": f"weights rotated over {copies} distinct copies ({copies * shard_bytes / 1e6:.0f} MB per rank, "
                              f"more than twice the {L2_BYTES / 1e6:.0f} MB L2) so every step reads HBM",
                        "weights": "declared constant (b200q_set_weights_constant): requested before the previous kernel has finished",
@@ -745,6 +766,7 @@ def main():
                        "parallelism": f"n-shard x{world}"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "prefill": prefill, "moe": moe,
             "parity": parity, "cpu_baseline": cpu_baseline, "device_status": list(status), "e2e_max_abs_gap": e2e_gap,
+            "ms_per_step_dependent_chain": ms_dependent,
         }
         print(json.dumps(line))
     if world > 1:

@@ -275,14 +275,19 @@ int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uin
  * kernel waits inside (its weight stream starts meanwhile, so a chain of sharded layers costs
  * one launch per layer); in front of the other kernels the wait is launched on its own.  The
  * last step of a chain still needs b200q_peer_wait before its result is used.  Same bound and
- * status code as b200q_peer_wait.
+ * status code as b200q_peer_wait.  wait_before_x = 1 when x is the gathered output of the previous
+ * step (a stack of sharded layers feeding each other); 0 when x comes from elsewhere (replicated
+ * input, the output of another exchange that was waited for): then only the stores into the
+ * exchange buffers wait, which guards the reuse of a buffer the other ranks' consumers of the
+ * step before may still read, and the kernel's loads and products overlap the previous exchange.
  * The exchange these replace: AllGather::eval_gpu (mlx/backend/cuda/distributed.cu:57-83).
  */
 int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                              void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
                              int64_t M, int64_t N_local, int64_t K, int group_size, int bits,
                              uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                             const uint32_t* wait_flag_local, void* ws, size_t ws_bytes, void* stream);
+                             const uint32_t* wait_flag_local, int wait_before_x, void* ws, size_t ws_bytes,
+                             void* stream);
 int b200q_gather_qmm_sharded_signal(const void* x, const uint32_t* wq_local, const void* scales_local,
                                     const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
                                     int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,

@@ -240,7 +240,7 @@ long long g_peer_wait_limit = 2000000000ll;
 int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
                  int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
                  int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                 const uint32_t* wait_flag, void* ws, size_t ws_bytes, void* stream);
+                 const uint32_t* wait_flag, int wait_before_x, void* ws, size_t ws_bytes, void* stream);
 }  // namespace
 
 extern "C" void b200q_set_peer_wait_limit_ms(int ms) {
@@ -252,25 +252,25 @@ extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* 
                                  int64_t N_local, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
                                  void* stream) {
   return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, nullptr,
-                      nullptr, nullptr, nullptr, ws, ws_bytes, stream);
+                      nullptr, nullptr, nullptr, 0, ws, ws_bytes, stream);
 }
 
 extern "C" int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                                         void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M,
                                         int64_t N_local, int64_t K, int group_size, int bits, uint32_t* const* flag_peers,
                                         uint32_t* epoch_local, uint32_t* counter_local, const uint32_t* wait_flag_local,
-                                        void* ws, size_t ws_bytes, void* stream) {
+                                        int wait_before_x, void* ws, size_t ws_bytes, void* stream) {
   if (!flag_peers || !epoch_local || !counter_local)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null flag list, epoch or counter");
   return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, flag_peers,
-                      epoch_local, counter_local, wait_flag_local, ws, ws_bytes, stream);
+                      epoch_local, counter_local, wait_flag_local, wait_before_x, ws, ws_bytes, stream);
 }
 
 namespace {
 int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
                  int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
                  int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                 const uint32_t* wait_flag, void* ws, size_t ws_bytes, void* stream) {
+                 const uint32_t* wait_flag, int wait_before_x, void* ws, size_t ws_bytes, void* stream) {
   if (!y_peers || n_peers < 1 || n_peers > kMaxPeers)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] between 1 and %d output buffers are supported (got %d)", kMaxPeers, n_peers);
   if (ld < N_local || col0 < 0 || col0 + N_local > ld)
@@ -304,6 +304,7 @@ int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const vo
     if (rows) {
       a.peers.sig.wait_flag = wait_flag;
       a.peers.sig.wait_limit = g_peer_wait_limit;
+      a.peers.sig.wait_x = wait_before_x ? 1 : 0;
     } else {
       uint32_t* status = (ws && ws_bytes >= kStatusBytes)
                              ? reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + ws_bytes - kStatusBytes) : nullptr;

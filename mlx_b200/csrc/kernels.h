@@ -26,6 +26,10 @@ struct PeerSignal {
   // has finished the previous exchange step (bounded by wait_limit SM cycles, then status 6).
   const uint32_t* wait_flag;
   long long wait_limit;
+  // 1: x is the gathered output of the previous step, so x is not read before the flag either;
+  // 0: x comes from elsewhere and only the stores wait (they reuse a buffer the previous step's
+  // consumers on other ranks may still be reading).
+  int wait_x;
 };
 struct PeerOut {
   void* y[kMaxPeers];

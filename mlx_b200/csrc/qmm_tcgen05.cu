@@ -9,11 +9,11 @@
 // to 256 tokens per instruction, and the operand that streams unchanged (x) is B.
 //
 //   thread A: TMA  --packed W tile [128 rows x 128 k, 16*bits bytes per row]-->  smem ring P
-//   16 dequant warps in two sets of 8 (even / odd 64-k blocks): one thread per weight row
-//        (= one TMEM lane): unpack 32 k with shift/lop3/prmt, apply s*q+b in bf16x2,
-//        tcgen05.st into the A ring in TMEM.  The unpack of one block is a chain of
-//        dependent ALU work; four dequant warps per SM sub-partition keep its pipes busy
-//   thread B: TMA  --x tile [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
+//   16 dequant warps (4 TMEM lane quadrants x 4 quarters of the 128-k stage): one thread per
+//        weight row (= one TMEM lane) unpacks 32 k, applies s*q+b in bf16x2 (4- and 8-bit:
+//        mask + one fma on the field read as a subnormal bf16; other widths shift/lop3/prmt),
+//        tcgen05.st into the A ring in TMEM; scales and biases come as 16-byte chunks per row
+//   thread B: TMA  --two x sub-tiles [NT tokens x 64 k], 128B-swizzled K-major-->  smem ring B
 //   1 thread: tcgen05.mma.kind::f16 (A from TMEM, B from smem descriptors), fp32
 //        accumulator [128 lanes x NT columns] in TMEM, tcgen05.commit on mbarriers
 //   8 epilogue warps (two per TMEM lane quadrant, half of the token columns each):
@@ -27,9 +27,15 @@
 // every NT-row slice of the expert-sorted activations; the weight tensor map spans the
 // stacked experts [E*N, K*bits/8].
 //
-// TMEM columns (512 allocated): [0, 256) accumulator, [256, 512) A ring of 8 stages
-// (64 k of bf16 = 32 columns each).  One CTA per SM (persistent), tiles are taken
+// TMEM columns (512 allocated): [0, 256) accumulator, [256, 512) A ring of 4 stages
+// (128 k of bf16 = 64 columns each).  One CTA per SM (persistent), tiles are taken
 // round-robin; no CTA ever waits on another CTA.
+//
+// A pipeline stage is 128 k: the MMA-issuing thread is blocked while the tensor pipe is busy
+// (the queue behind tcgen05.mma is about one instruction deep; an M=128, K=16 instruction
+// takes 128 cycles at N=256 and no less than about 100 at any smaller N) and pays about 65
+// cycles for every tcgen05.commit, so every wait and commit per stage is time the tensor pipe
+// idles: eight MMAs per pair of commits instead of four.
 //
 // Every mbarrier wait is bounded.  When a wait expires the role sets the CTA abort
 // flag and the device status word, all roles leave their loops, TMEM is released and

@@ -430,7 +430,7 @@ qmv_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
   // ================================= consumer warps ===========================================
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsConsumer));
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (p.sig.wait_flag != nullptr) {   // x is the gathered output of the previous exchange step
+  if (p.sig.wait_flag != nullptr && p.sig.wait_x) {   // x is the gathered output of the previous exchange step
     if (lane == 0) peer_wait_previous(p.sig, p.status);
     __syncwarp();
   }

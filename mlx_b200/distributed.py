@@ -220,15 +220,18 @@ class PeerOutput:
 
 
 def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tensor, out: PeerOutput,
-                             chained: bool = False) -> torch.Tensor:
+                             chained=False) -> torch.Tensor:
     """y = x @ dequant(W)^T for the full W, every rank holding only its rows: one matmul launch
     whose epilogue stores to all ranks and whose last thread block updates the flags, and one
     bounded wait (`out.check()` tells whether it ran out).
 
-    chained=True is for a chain of sharded layers on one stream: the call waits, before it reads x
-    or stores its result, until every rank has finished the PREVIOUS call's exchange (inside the
-    decode kernel, whose weight stream starts meanwhile) and does not wait for its own; the caller
-    ends the chain with `out.wait()` before the last result is used.  x: [M, K] bf16 CUDA,
+    chained=True is for a chain of sharded layers on one stream whose x is the previous call's
+    gathered output: the call waits, before it reads x or stores its result, until every rank has
+    finished the PREVIOUS call's exchange (inside the decode kernel, whose weight stream starts
+    meanwhile) and does not wait for its own; the caller ends the chain with `out.wait()` before
+    the last result is used.  chained="buffers" is the same for calls whose x comes from elsewhere
+    (a replicated input, another exchange that was waited for): only the stores into the exchange
+    buffers wait, so loads and products overlap the previous exchange.  x: [M, K] bf16 CUDA,
     the same on every rank.  Returns this rank's [M, N] view (valid until the buffer is used again
     two calls later)."""
     if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
@@ -249,7 +252,7 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
                                             layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
                                             ctypes.c_void_p(out.counter),
                                             ctypes.c_void_p(out.flag[out.rank] if (chained and out.step > 0) else 0),
-                                            vp(ws), ws.numel(), st))
+                                            0 if chained == "buffers" else 1, vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
     if not chained:
@@ -367,7 +370,7 @@ def sharded_matmul_allreduce(layer: QuantizedShardedToAllLinear, x: torch.Tensor
     ys = (ctypes.c_void_p * R)(*[b + buf * out.buf_bytes + out.rank * slot_bytes for b in out.base])
     _lib.check(lib.b200q_qmm_sharded_signal(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M,
                                             N, K, layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
-                                            ctypes.c_void_p(out.counter), ctypes.c_void_p(0), vp(ws), ws.numel(), st))
+                                            ctypes.c_void_p(out.counter), ctypes.c_void_p(0), 0, vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)

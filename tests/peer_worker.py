@@ -42,6 +42,33 @@ def main():
         dist.barrier()
     out.close()
 
+    # ---- a chain of sharded layers on the row-owning decode kernel (K a multiple of 16 groups): every
+    # call's x is the gathered output of the previous one, the wait for it runs inside the consuming
+    # kernel, the host waits once at the end.  Checked against the oracle applied layer by layer.
+    Nc = Kc = 2048
+    wqc, sc_, bc_ = O.quantize(make_w(6, (Nc, Kc), "bf16", std=0.03), g, 4, "bf16")
+    chain = QuantizedAllToShardedLinear(u32_to_torch(wqc), to_torch(sc_, "bf16"), to_torch(bc_, "bf16"), g, 4,
+                                        rank=rank, world=world)
+    assert mb.qmm_kernel_name(torch.bfloat16, 16, Nc // world, Kc, g, 4) == "qmv_rows"
+    outc = PeerOutput(16, Nc)
+    for trial, M in enumerate((16, 5)):
+        x0 = make_x(60 + trial, (M, Kc), "bf16")
+        depth = 4
+        h = to_torch(x0, "bf16")
+        for _ in range(depth):
+            h = sharded_matmul_allgather(chain, h, outc, chained=True)
+        outc.wait()
+        torch.cuda.synchronize()
+        outc.check()
+        ref_h = x0
+        for _ in range(depth):
+            ref_h = O.to_dtype(O.qmm_f32_from(ref_h, wqc, sc_, bc_, "bf16", transpose=True, group_size=g, bits=4), "bf16")
+        good, rel = qmm_close(O.to_f32(from_torch(h.contiguous()), "bf16"), O.to_f32(ref_h, "bf16"), 3e-2)
+        print(f"rank {rank} chain M={M} depth={depth} ok={good} rel={rel:.4f}", flush=True)
+        ok = ok and good
+        dist.barrier()
+    outc.close()
+
     # ---- expert-parallel gather_qmm: 8 experts over the ranks, 40 tokens, top-2
     E, tokens, topk, N2, K2 = 8, 40, 2, 256, 512
     wq2, s2, b2 = O.quantize(make_w(7, (E, N2, K2), "bf16"), g, 4, "bf16")

@@ -240,6 +240,30 @@ def test_tcgen05_all_bit_widths(bits, g):
     run_case("bf16", 512, 256, 1024, g, bits, seed=bits, expect_kernel=("qmm_tcgen05",))
 
 
+@pytest.mark.parametrize("bits", (4, 8, 3))
+@pytest.mark.parametrize("M", (8, 96))
+def test_rows_of_very_different_magnitude(bits, M):
+    """Weight rows spanning 2^-24 .. 2^8 in magnitude, some all zero: the prefill kernel's unpack has
+    a form for scales whose exponent leaves room for a factor 2^133 and a general form for the
+    others, and both meet inside one warp here; the decode kernels see the same matrix (M = 8).
+    Tolerance per output column: 1e-2 (|y_ref| + ||w_n|| rms(x))."""
+    dtype, N, K, g = "bf16", 384, 1024, 64
+    rng = np.random.default_rng(40 + bits)
+    wf = rng.standard_normal((N, K)).astype(np.float32) * (2.0 ** rng.integers(-24, 9, size=(N, 1))).astype(np.float32)
+    wf[5] = 0.0
+    wf[200, :512] = 0.0
+    w = O.to_dtype(wf, dtype)
+    wq, s, b = O.quantize(w, g, bits, dtype)
+    x = make_x(41, (M, K), dtype)
+    ref = O.qmm_f32_from(x, wq, s, b, dtype, transpose=True, group_size=g, bits=bits)
+    y = mb.quantized_matmul(to_torch(x, dtype), u32_to_torch(wq), to_torch(s, dtype), to_torch(b, dtype),
+                            group_size=g, bits=bits)
+    cs = col_scale(wq, s, b, x, dtype, g, bits)
+    ok, rel = qmm_close(O.to_f32(from_torch(y), dtype), ref, 1e-2, cs[None, :])
+    assert ok, rel
+    assert not from_torch(y)[:, 5].any()
+
+
 def test_ragged_k_falls_back_to_generic():
     run_case("bf16", 40, 96, 192, 32, 4, seed=1, expect_kernel=("qmm_generic",))
 
