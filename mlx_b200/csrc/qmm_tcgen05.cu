@@ -556,6 +556,13 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         uint32_t v[32];
         tcgen05_ld_x32(tmem_acc + lane_field + c, v);
         tcgen05_wait_ld();
+        if (c + 32 >= c_end) {
+          // the last chunk is in registers: the accumulator is free for the next tile's MMAs while
+          // this chunk is converted and stored
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+        }
         const int lim = (tc_.rows < c_end ? tc_.rows : c_end) - c;  // valid columns of this chunk
         if (n < p.N && lim > 0) {
           if (p.dst_row == nullptr) {
@@ -578,9 +585,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           }
         }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+      if (c_begin >= c_end) {   // no column of this tile for this warp: release at once
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+      }
     }
     if (warp == 2 + kDequantWarps) { TC_OUT(12, pw0); TC_OUT(13, clock64() - prof_entry); }
   }
