@@ -280,14 +280,18 @@ int b200q_peer_wait(const uint32_t* flag_local, const uint32_t* epoch_local, uin
  * input, the output of another exchange that was waited for): then only the stores into the
  * exchange buffers wait, which guards the reuse of a buffer the other ranks' consumers of the
  * step before may still read, and the kernel's loads and products overlap the previous exchange.
+ * self = index of this rank's own buffer in y_peers, or -1 if unknown.  When known, a prefill-size
+ * result over more than four ranks is stored locally by the product and moved to the other ranks by
+ * a copy kernel with 16-byte accesses (the tensor-core epilogue's peer stores are 64-byte warp
+ * stores per destination and take longer than the product there); the copy kernel signals.
  * The exchange these replace: AllGather::eval_gpu (mlx/backend/cuda/distributed.cu:57-83).
  */
 int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                              void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype,
                              int64_t M, int64_t N_local, int64_t K, int group_size, int bits,
                              uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                             const uint32_t* wait_flag_local, int wait_before_x, void* ws, size_t ws_bytes,
-                             void* stream);
+                             const uint32_t* wait_flag_local, int wait_before_x, int self, void* ws,
+                             size_t ws_bytes, void* stream);
 int b200q_gather_qmm_sharded_signal(const void* x, const uint32_t* wq_local, const void* scales_local,
                                     const void* biases_local, const uint32_t* lhs_idx, const uint32_t* rhs_idx,
                                     int64_t n_idx, void* const* y_peers, int n_peers, int self, int dtype,

@@ -45,7 +45,7 @@ SIGNATURES = {
     "b200q_gather_qmm_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
                                       _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "b200q_qmm_sharded_signal": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _i64, _i64, _i64, _i, _i, _vp, _vp, _vp,
-                                      _vp, _i, _vp, _sz, _vp]),
+                                      _vp, _i, _i, _vp, _sz, _vp]),
     "b200q_gather_qmm_sharded_signal": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i, _i, _i, _i64, _i64, _i64, _i64,
                                              _i64, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200q_set_peer_wait_limit_ms": (None, [_i]),

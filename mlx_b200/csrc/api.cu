@@ -230,17 +230,49 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const T* __restrict__ 
   }
   for (int j = 0; j < 8 && i0 + j < n; ++j) y[i0 + j] = Elem<T>::from_float(acc[j]);
 }
+// Copies this rank's block of a finished [M, ld] result (columns [col0, col0 + n_cols)) from its own
+// buffer into the buffers of the other ranks with 16-byte loads and stores, then signals.  The
+// tensor-core kernel's own peer stores are 64-byte warp stores issued once per destination from
+// its epilogue; with more than four ranks they take longer than the product, so the product then
+// stores locally only and this kernel moves the block.
+struct PushParams {
+  char* y[kMaxPeers];
+  int n, self;
+  int64_t row_bytes, col_bytes, chunks_per_row, total;   // pitch, byte offset of the block, 16-byte chunks
+  PeerSignal sig;
+};
+__global__ void __launch_bounds__(256) peer_push_kernel(const PushParams p) {
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < p.total; u += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = u / p.chunks_per_row, c = u - m * p.chunks_per_row;
+    const int64_t off = m * p.row_bytes + p.col_bytes + c * 16;
+    const uint4 v = *reinterpret_cast<const uint4*>(p.y[p.self] + off);
+    for (int q = 0; q < p.n; ++q)
+      if (q != p.self) *reinterpret_cast<uint4*>(p.y[q] + off) = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) peer_signal_tail(p.sig);
+}
 }  // namespace peer
 }  // namespace b200q
 
 namespace {
+// B200Q_PUSH=0: never the separate push; 1: whenever it is possible (testing); default: above four ranks
+// (measured on M=4096, N=14336: 2 ranks 271 us fused / 326 us pushed, 4 ranks 272 / 281, 8 ranks 391 / 254).
+int push_mode() {
+  static int v = -2;
+  if (v == -2) {
+    const char* e = getenv("B200Q_PUSH");
+    v = e ? atoi(e) : -1;
+  }
+  return v;
+}
 // Bound of b200q_peer_wait in SM clock cycles (default about one second).
 long long g_peer_wait_limit = 2000000000ll;
 
 int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
                  int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
                  int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                 const uint32_t* wait_flag, int wait_before_x, void* ws, size_t ws_bytes, void* stream);
+                 const uint32_t* wait_flag, int wait_before_x, int self, void* ws, size_t ws_bytes, void* stream);
 }  // namespace
 
 extern "C" void b200q_set_peer_wait_limit_ms(int ms) {
@@ -252,25 +284,25 @@ extern "C" int b200q_qmm_sharded(const void* x, const uint32_t* wq, const void* 
                                  int64_t N_local, int64_t K, int group_size, int bits, void* ws, size_t ws_bytes,
                                  void* stream) {
   return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, nullptr,
-                      nullptr, nullptr, nullptr, 0, ws, ws_bytes, stream);
+                      nullptr, nullptr, nullptr, 0, -1, ws, ws_bytes, stream);
 }
 
 extern "C" int b200q_qmm_sharded_signal(const void* x, const uint32_t* wq, const void* scales, const void* biases,
                                         void* const* y_peers, int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M,
                                         int64_t N_local, int64_t K, int group_size, int bits, uint32_t* const* flag_peers,
                                         uint32_t* epoch_local, uint32_t* counter_local, const uint32_t* wait_flag_local,
-                                        int wait_before_x, void* ws, size_t ws_bytes, void* stream) {
+                                        int wait_before_x, int self, void* ws, size_t ws_bytes, void* stream) {
   if (!flag_peers || !epoch_local || !counter_local)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] null flag list, epoch or counter");
   return sharded_impl(x, wq, scales, biases, y_peers, n_peers, ld, col0, dtype, M, N_local, K, group_size, bits, flag_peers,
-                      epoch_local, counter_local, wait_flag_local, wait_before_x, ws, ws_bytes, stream);
+                      epoch_local, counter_local, wait_flag_local, wait_before_x, self, ws, ws_bytes, stream);
 }
 
 namespace {
 int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const void* biases, void* const* y_peers,
                  int n_peers, int64_t ld, int64_t col0, int dtype, int64_t M, int64_t N_local, int64_t K,
                  int group_size, int bits, uint32_t* const* flag_peers, uint32_t* epoch_local, uint32_t* counter_local,
-                 const uint32_t* wait_flag, int wait_before_x, void* ws, size_t ws_bytes, void* stream) {
+                 const uint32_t* wait_flag, int wait_before_x, int self, void* ws, size_t ws_bytes, void* stream) {
   if (!y_peers || n_peers < 1 || n_peers > kMaxPeers)
     return fail(B200Q_ERR_INVALID_ARGUMENT, "[quantized_matmul_sharded] between 1 and %d output buffers are supported (got %d)", kMaxPeers, n_peers);
   if (ld < N_local || col0 < 0 || col0 + N_local > ld)
@@ -320,7 +352,37 @@ int sharded_impl(const void* x, const uint32_t* wq, const void* scales, const vo
     if (int rc = qmv_mma(a, st)) return rc;
     return signal_only();
   }
-  if (a.K > 0 && qmm_tc_supported(a)) return qmm_tc(a, st);                                // signals from its last block
+  if (a.K > 0 && qmm_tc_supported(a)) {
+    // Large results over more than four ranks: the product stores its block locally, a copy kernel
+    // moves it to the other ranks with 16-byte accesses and signals (see peer_push_kernel).
+    const int pm = push_mode();
+    const int64_t esz = 2;
+    bool push = flag_peers && self >= 0 && self < n_peers && n_peers >= 2 && pm != 0 && (pm == 1 || (n_peers > 4 && a.M >= 256));
+    push = push && (ld * esz) % 16 == 0 && (col0 * esz) % 16 == 0 && (N_local * esz) % 16 == 0;
+    for (int q = 0; push && q < n_peers; ++q) push = (reinterpret_cast<uintptr_t>(y_peers[q]) & 15) == 0;
+    if (!push) return qmm_tc(a, st);                                                         // signals from its last block
+    const PeerSignal sig = a.peers.sig;
+    a.peers.n = 1;
+    a.peers.y[0] = y_peers[self];
+    a.peers.sig = PeerSignal{};
+    if (int rc = qmm_tc(a, st)) return rc;
+    peer::PushParams pp{};
+    for (int q = 0; q < n_peers; ++q) pp.y[q] = static_cast<char*>(y_peers[q]);
+    pp.n = n_peers; pp.self = self;
+    pp.row_bytes = ld * esz; pp.col_bytes = col0 * esz;
+    pp.chunks_per_row = N_local * esz / 16;
+    pp.total = a.M * pp.chunks_per_row;
+    pp.sig = sig;
+    pp.sig.wait_flag = nullptr;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t blocks = (pp.total + 255) / 256;
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;
+    peer::peer_push_kernel<<<(unsigned)blocks, 256, 0, st>>>(pp);
+    B200Q_LAUNCH_OK("peer_push_kernel");
+    return B200Q_OK;
+  }
   return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul_sharded] only bfloat16 with K a multiple of 128 has a peer-store epilogue");
 }
 }  // namespace

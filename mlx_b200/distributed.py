@@ -252,7 +252,7 @@ def sharded_matmul_allgather(layer: "QuantizedAllToShardedLinear", x: torch.Tens
                                             layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
                                             ctypes.c_void_p(out.counter),
                                             ctypes.c_void_p(out.flag[out.rank] if (chained and out.step > 0) else 0),
-                                            0 if chained == "buffers" else 1, vp(ws), ws.numel(), st))
+                                            0 if chained == "buffers" else 1, out.rank, vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
     if not chained:
@@ -370,7 +370,7 @@ def sharded_matmul_allreduce(layer: QuantizedShardedToAllLinear, x: torch.Tensor
     ys = (ctypes.c_void_p * R)(*[b + buf * out.buf_bytes + out.rank * slot_bytes for b in out.base])
     _lib.check(lib.b200q_qmm_sharded_signal(vp(xs), vp(layer.weight), vp(layer.scales), vp(layer.biases), ys, R, N, 0, dt, M,
                                             N, K, layer.group_size, layer.bits, out.flag_ptrs(), ctypes.c_void_p(out.epoch),
-                                            ctypes.c_void_p(out.counter), ctypes.c_void_p(0), 0, vp(ws), ws.numel(), st))
+                                            ctypes.c_void_p(out.counter), ctypes.c_void_p(0), 0, -1, vp(ws), ws.numel(), st))
     out.step += 1
     out._ws = ws
     status = ctypes.c_void_p(ws.data_ptr() + ws.numel() - 16)
