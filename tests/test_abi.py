@@ -67,6 +67,8 @@ def test_kernel_selection_names():
     assert name(1, 4096, 4096) == "qmv_rows"
     assert name(16, 14336, 4096) == "qmv_rows"
     assert name(16, 14336, 4096, bits=3) == "qmv_mma"
+    assert name(17, 14336, 4096) == "qmv_rows" and name(32, 14336, 4096) == "qmv_rows"   # two passes of up to 16 rows
+    assert name(33, 14336, 4096) == "qmm_tcgen05" and name(17, 14336, 4096, bits=3) == "qmm_tcgen05"
     assert name(16, 14336, 4096, dt=_lib.F32) == "qmm_generic"
     assert name(16, 4096, 4096, tr=0) == "qmm_generic"
     assert name(1, 4096, 4096, tr=0) == "qvm" and name(4, 4096, 4096, tr=0, bits=8) == "qvm"
