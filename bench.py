@@ -22,7 +22,7 @@ N > 1; `moe` the Mixtral-style gather_qmm configuration (experts split over the 
 from every rank's block - agree with the CPU checker; `cpu_baseline` times the reference
 project's own CPU code.  `--config all` first prints one line per case of the other named
 configurations (GEMV, bit-width / group sweep with quantize / dequantize, non-transposed
-decode), each with its own parity verdict.  `--impl reference` times only the reference CPU
+decode), each with its own parity result.  `--impl reference` times only the reference CPU
 code (all host cores) and prints its own line.
 """
 from __future__ import annotations
@@ -231,7 +231,7 @@ def graph_time(fn, iters, stream, torch):
 # ------------------------------------------------------------------------ other named configurations
 def sweep_cases(lib, _lib, mb, torch, dev, quick=False):
     """One JSON line per case of the configurations other than the headline one, each with a
-    parity verdict against the CPU checker (one GPU; run by --config all on rank 0)."""
+    parity result against the CPU checker (one GPU; run by --config all on rank 0)."""
     import oracle as O
     hbm, tf, src = measured_peaks()
     P = lambda t: ctypes.c_void_p(t.data_ptr())
