@@ -204,6 +204,14 @@ def oracle_columns(w_rows_bf16: np.ndarray, x_bf16: np.ndarray, bits=BITS, group
     return O.qmm_f32_from(x_bf16, wq, s, b, "bf16", transpose=True, group_size=group, bits=bits)
 
 
+def queue_delay(torch, stream):
+    """About 100 us of spinning queued on `stream` ahead of a start event: the work that follows is
+    already enqueued when the event's time is taken, so the interval holds device time only, not the
+    host's launch latency (which is as long as several steps of this workload)."""
+    with torch.cuda.stream(stream):
+        torch.cuda._sleep(200000)
+
+
 def graph_time(fn, iters, stream, torch):
     """Seconds per call of fn(i): `iters` calls captured in one CUDA graph, best of three replays."""
     with torch.cuda.stream(stream):
@@ -219,6 +227,7 @@ def graph_time(fn, iters, stream, torch):
     best = 1e30
     for _ in range(3):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             e0.record(stream)
             g.replay()
@@ -486,6 +495,8 @@ def main():
         barrier()
         sampler.start()
         time.sleep(0.3)
+        barrier()
+        queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             e0.record(stream)
             graph.replay()
@@ -495,6 +506,7 @@ def main():
         sampler.start()
         time.sleep(0.3)
         barrier()
+        queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             e0.record(stream)
             for i in range(args.steps):
@@ -520,6 +532,7 @@ def main():
         g2.replay()
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             f0.record(stream)
             g2.replay()
@@ -762,7 +775,8 @@ def main():
                        "l2": f"weights rotated over {copies} distinct copies ({copies * shard_bytes / 1e6:.0f} MB per rank, "
                              f"more than twice the {L2_BYTES / 1e6:.0f} MB L2) so every step reads HBM",
                        "weights": "declared constant (b200q_set_weights_constant): requested before the previous kernel has finished",
-                       "timing": "CUDA events on the launching stream" + (", steps replayed from one CUDA graph" if graphed else ""),
+                       "timing": "CUDA events on the launching stream" + (", steps replayed from one CUDA graph" if graphed else "")
+                                 + "; a 100 us delay kernel is queued ahead of the start event, so the interval holds device time only",
                        "parallelism": f"n-shard x{world}"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "prefill": prefill, "moe": moe,
             "parity": parity, "cpu_baseline": cpu_baseline, "device_status": list(status), "e2e_max_abs_gap": e2e_gap,
