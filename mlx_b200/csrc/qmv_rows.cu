@@ -47,6 +47,7 @@ namespace {
 using tc::mbar_init;
 using tc::mbar_expect_tx;
 using tc::mbar_wait;
+using tc::mbar_test;   // non-blocking look at a barrier phase (try_wait may park the thread before it says no)
 using tc::smem_u32;
 
 constexpr int kConsumers = 16;                   // warps that multiply; one K slice each
@@ -76,18 +77,6 @@ __device__ unsigned int g_rows_launch_in, g_rows_launch_out;
 #define RP_MARK(i)
 #endif
 
-// Non-blocking look at a barrier phase (try_wait may park the thread for a while before it says no).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
