@@ -60,7 +60,8 @@ __host__ __device__ constexpr int stages_p(int bits) { return bits <= 4 ? 4 : (b
 constexpr size_t kSmemMax = 227 * 1024;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
-constexpr int kDequantWarps = 16;   // 4 TMEM lane quadrants x 4 quarters (32 k) of a stage
+constexpr int kDequantWarps = 16;   // two sets of 8: 4 TMEM lane quadrants x 2 halves (64 k) of a stage
+constexpr int kDequantSet = 8;      // set 0 unpacks the even stages of a tile, set 1 the odd ones
 constexpr int kEpilogueWarps = 8;   // two per TMEM lane quadrant, each drains half of the columns
 constexpr int kProducerPWarp = 2 + kDequantWarps + kEpilogueWarps;  // last warp
 constexpr int kThreads = 32 * (3 + kDequantWarps + kEpilogueWarps);  // 864
@@ -297,9 +298,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   const int total_tiles = p.mtiles ? *p.n_mtiles * p.n_tiles : p.n_tiles * p.m_tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStagesP; ++i) { mbar_init(smem_u32(&bars->full_p[i]), 1); mbar_init(smem_u32(&bars->empty_p[i]), kDequantWarps); }
+    for (int i = 0; i < kStagesP; ++i) { mbar_init(smem_u32(&bars->full_p[i]), 1); mbar_init(smem_u32(&bars->empty_p[i]), kDequantSet); }
     for (int i = 0; i < kStagesB; ++i) { mbar_init(smem_u32(&bars->full_b[i]), 1); mbar_init(smem_u32(&bars->empty_b[i]), 1); }
-    for (int i = 0; i < kStagesA; ++i) { mbar_init(smem_u32(&bars->full_a[i]), kDequantWarps); mbar_init(smem_u32(&bars->empty_a[i]), 1); }
+    for (int i = 0; i < kStagesA; ++i) { mbar_init(smem_u32(&bars->full_a[i]), kDequantSet); mbar_init(smem_u32(&bars->empty_a[i]), 1); }
     mbar_init(smem_u32(&bars->acc_full), 1);
     mbar_init(smem_u32(&bars->acc_empty), kEpilogueWarps);
     bars->abort_flag = 0;
@@ -404,13 +405,18 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     }
   } else if (warp < 2 + kDequantWarps) {
     // ------------------------------------------------------------ dequant: one thread per weight row
+    // A warp's trip through one stage (wait for the packed tile, unpack, publish, wait for a free
+    // A stage, store) is a chain of dependent latencies of about the length of a stage's MMAs; with
+    // every warp on every stage that chain bounded the kernel.  So the warps form two sets that
+    // take alternate stages, 64 k per thread and stage: each set has two stage times per trip.
     const int dq = warp - 2;
+    const int dset = dq >> 3;            // stages ks = dset (mod 2) of every tile are this warp's
     const int quad = warp & 3;           // TMEM lane quadrant this warp may access
-    const int kq = dq >> 2;              // which 32-k quarter of the 128-k stage
+    const int half = (dq >> 2) & 1;      // which 64-k half of the 128-k stage
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     const int row_groups = p.K >> (5 + p.group_shift);
-    uint32_t sa = 0, pa = 0, sp = 0, pp = 0;
+    uint32_t tcount = 0;                 // tiles done: the stage counter of (tile, ks) is tcount * kstages + ks
     // The arrival for an A stage is deferred until the next stage has been unpacked, so the
     // latency of the tensor-memory store overlaps the next block's ALU work.
     bool pending = false;
@@ -455,82 +461,87 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       const int row = row_of(tile);
       const unsigned short* sc = reinterpret_cast<const unsigned short*>(p.scales) + (size_t)row * row_groups;
       const unsigned short* bi = reinterpret_cast<const unsigned short*>(p.biases) + (size_t)row * row_groups;
-      uint32_t s_next = 0, b_next = 0;
-      if (!vec) {
-        s_next = __ldg(sc + ((kq * 32) >> gs5));
-        b_next = __ldg(bi + ((kq * 32) >> gs5));
-      }
       cur_chunk = -1;
-      for (int ks = 0; ks < kstages; ++ks) {
-        uint32_t s_cur = s_next, b_cur = b_next;
+      for (int ks = dset; ks < kstages; ks += 2) {
+        const uint32_t it = tcount * (uint32_t)kstages + (uint32_t)ks;
+        const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1u;
+        const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1u;
+        // scale and bias of the two 32-k quarters of this thread's half (one group or two)
+        uint32_t s_q[2], b_q[2];
         if (vec) {
-          const int g = (ks * kStageK + kq * 32) >> gs5;
-          if ((g >> 3) != cur_chunk) {
+          const int g0 = (ks * kStageK + half * 64) >> gs5, g1 = (ks * kStageK + half * 64 + 32) >> gs5;
+          if ((g0 >> 3) != cur_chunk) {
             s_cur4 = s_nxt4; b_cur4 = b_nxt4;
-            cur_chunk = g >> 3;
+            cur_chunk = g0 >> 3;
             prefetch();
           }
-          s_cur = pick(s_cur4, g & 7);
-          b_cur = pick(b_cur4, g & 7);
+          s_q[0] = pick(s_cur4, g0 & 7); b_q[0] = pick(b_cur4, g0 & 7);
+          s_q[1] = g1 == g0 ? s_q[0] : pick(s_cur4, g1 & 7);
+          b_q[1] = g1 == g0 ? b_q[0] : pick(b_cur4, g1 & 7);
+        } else {
+          const int g0 = (ks * kStageK + half * 64) >> gs5, g1 = (ks * kStageK + half * 64 + 32) >> gs5;
+          s_q[0] = __ldg(sc + g0); b_q[0] = __ldg(bi + g0);
+          s_q[1] = __ldg(sc + g1); b_q[1] = __ldg(bi + g1);
         }
         TC_T0();
         if (!TC_WAIT16(smem_u32(&bars->full_p[sp]), pp, abort_flag)) { ok = false; break; }
         TC_ACC(pw0);
-        // this thread's 32 fields: BITS words at quarter kq of its row
-        uint32_t w[BITS];
-        {
-          const unsigned char* src = ring_p + sp * kPStageBytes + row_in_tile * kPRowBytes + kq * (4 * BITS);
-          if constexpr (BITS == 4) {
-            const uint4 v = *reinterpret_cast<const uint4*>(src);
-            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-          } else if constexpr (BITS == 8) {
-            const uint4 v = *reinterpret_cast<const uint4*>(src), u = *reinterpret_cast<const uint4*>(src + 16);
-            w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; w[4] = u.x; w[5] = u.y; w[6] = u.z; w[7] = u.w;
-          } else if constexpr (BITS == 2 || BITS == 6) {
+        const unsigned char* src0 = ring_p + sp * kPStageBytes + row_in_tile * kPRowBytes + half * (8 * BITS);
+        bool freed = false;
 #pragma unroll
-            for (int i = 0; i < BITS / 2; ++i) {
-              const uint2 v = *reinterpret_cast<const uint2*>(src + 8 * i);
-              w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        for (int q = 0; q < 2; ++q) {
+          // this thread's 32 fields of quarter 2 * half + q: BITS words of its row
+          uint32_t w[BITS];
+          {
+            const unsigned char* src = src0 + q * (4 * BITS);
+            if constexpr (BITS == 4) {
+              const uint4 v = *reinterpret_cast<const uint4*>(src);
+              w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+            } else if constexpr (BITS == 8) {
+              const uint4 v = *reinterpret_cast<const uint4*>(src), u = *reinterpret_cast<const uint4*>(src + 16);
+              w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; w[4] = u.x; w[5] = u.y; w[6] = u.z; w[7] = u.w;
+            } else if constexpr (BITS == 2 || BITS == 6) {
+#pragma unroll
+              for (int i = 0; i < BITS / 2; ++i) {
+                const uint2 v = *reinterpret_cast<const uint2*>(src + 8 * i);
+                w[2 * i] = v.x; w[2 * i + 1] = v.y;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < BITS; ++i) w[i] = *reinterpret_cast<const uint32_t*>(src + 4 * i);
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < BITS; ++i) w[i] = *reinterpret_cast<const uint32_t*>(src + 4 * i);
           }
-        }
-        uint32_t vals[16];
-        TC_T0();
-        dequant32<BITS>(w, s_cur, b_cur, vals);
+          uint32_t vals[16];
+          TC_T0();
+          dequant32<BITS>(w, s_q[q], b_q[q], vals);
 #ifdef B200Q_PROFILE
-        asm volatile("" ::"r"(vals[0]), "r"(vals[5]), "r"(vals[10]), "r"(vals[15]));
+          asm volatile("" ::"r"(vals[0]), "r"(vals[5]), "r"(vals[10]), "r"(vals[15]));
 #endif
-        TC_ACC(pw3);
-        // (scalar form, rows whose group count is not a multiple of eight) the next stage's scale
-        // and bias are requested after the unpack
-        if (!vec && ks + 1 < kstages) {
-          const int g = ((ks + 1) * kStageK + kq * 32) >> gs5;
-          s_next = __ldg(sc + g);
-          b_next = __ldg(bi + g);
+          TC_ACC(pw3);
+          if (q == 0) {
+            TC_T0();
+            if (pending) publish();
+            TC_ACC(pw1);
+            TC_T0();
+            if (!TC_WAIT16(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
+            TC_ACC(pw2);
+            tcgen05_fence_after();
+            freed = true;
+          }
+          TC_T0();
+          tcgen05_st_x16(tmem_a + lane_field + sa * 64 + (2 * half + q) * 16, vals);
+          TC_ACC(pw4);
         }
-        TC_T0();
-        if (pending) publish();
-        TC_ACC(pw1);
-        TC_T0();
-        if (!TC_WAIT16(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
-        TC_ACC(pw2);
-        tcgen05_fence_after();
-        TC_T0();
-        tcgen05_st_x16(tmem_a + lane_field + sa * 64 + kq * 16, vals);
-        TC_ACC(pw4);
+        if (!freed) break;
         pending = true;
         pending_sa = sa;
-        // The packed stage is released only here, after the store that consumes the unpacked
-        // registers has been issued: the shared-memory reads above have then returned for every
+        // The packed stage is released only here, after the stores that consume the unpacked
+        // registers have been issued: the shared-memory reads above have then returned for every
         // lane, so the refill of the stage cannot overtake them.
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->empty_p[sp]));
-        if (++sa == (uint32_t)kStagesA) { sa = 0; pa ^= 1; }
-        if (++sp == (uint32_t)kStagesP) { sp = 0; pp ^= 1; }
       }
+      ++tcount;
     }
     if (pending) publish();
     if (warp == 2) { TC_OUT(8, pw0); TC_OUT(9, pw1); TC_OUT(10, pw2); TC_OUT(11, clock64() - prof_entry); }
