@@ -417,16 +417,14 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     const int row_groups = p.K >> (5 + p.group_shift);
     uint32_t tcount = 0;                 // tiles done: the stage counter of (tile, ks) is tcount * kstages + ks
-    // The arrival for an A stage is deferred until the next stage has been unpacked, so the
-    // latency of the tensor-memory store overlaps the next block's ALU work.
-    bool pending = false;
-    uint32_t pending_sa = 0;
-    auto publish = [&]() {
+    // An A stage is published as soon as its stores have completed: each set has a stage time of
+    // slack, and the issuing thread gets the stage earlier than when the arrival waited for the
+    // next unpack (388 -> 382 us on M=4096).
+    auto publish = [&](uint32_t stage) {
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[pending_sa]));
-      pending = false;
+      if (lane == 0) mbar_arrive(smem_u32(&bars->full_a[stage]));
     };
     // Scales and biases: a thread needs one 2-byte value of each per stage, from a row of its own,
     // so a warp's load touches 32 cache lines whatever its width.  Fetched per stage they kept the
@@ -520,9 +518,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           TC_ACC(pw3);
           if (q == 0) {
             TC_T0();
-            if (pending) publish();
-            TC_ACC(pw1);
-            TC_T0();
             if (!TC_WAIT16(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
             TC_ACC(pw2);
             tcgen05_fence_after();
@@ -533,8 +528,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           TC_ACC(pw4);
         }
         if (!freed) break;
-        pending = true;
-        pending_sa = sa;
+        TC_T0();
+        publish(sa);
+        TC_ACC(pw1);
         // The packed stage is released only here, after the stores that consume the unpacked
         // registers have been issued: the shared-memory reads above have then returned for every
         // lane, so the refill of the stage cannot overtake them.
@@ -543,7 +539,6 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       }
       ++tcount;
     }
-    if (pending) publish();
     if (warp == 2) { TC_OUT(8, pw0); TC_OUT(9, pw1); TC_OUT(10, pw2); TC_OUT(11, clock64() - prof_entry); }
     TC_OUT(16 + dq, pw2); TC_OUT(32 + dq, pw0);
     if (warp == 2) { TC_OUT(48, pw3); TC_OUT(49, pw4); }
