@@ -58,6 +58,7 @@ constexpr int kMaxStagesP = 4;    // packed W tiles in shared memory
 // Packed stages: 16 * bits bytes per row and stage; next to three 64 KB x stages 35 KB remain.
 __host__ __device__ constexpr int stages_p(int bits) { return bits <= 4 ? 4 : (bits == 5 ? 3 : 2); }
 constexpr size_t kSmemMax = 227 * 1024;
+constexpr int kDoneRing = 12;
 constexpr int kAccCols = 256;
 constexpr int kTmemCols = 512;
 constexpr int kDequantWarps = 16;   // two sets of 8: 4 TMEM lane quadrants x 2 halves (64 k) of a stage
@@ -130,8 +131,13 @@ struct TcParams {
 
 struct __align__(8) Barriers {
   uint64_t full_p[kMaxStagesP], empty_p[kMaxStagesP];
-  uint64_t full_b[kMaxStagesB], empty_b[kMaxStagesB];
-  uint64_t full_a[kStagesA], empty_a[kStagesA];
+  uint64_t full_b[kMaxStagesB];
+  uint64_t full_a[kStagesA];
+  // One commit per stage: stage `it` (counted across tiles) arrives on done[it % kDoneRing] when its
+  // MMAs have completed.  The A slot it % 4 and the x slot it % nsb are free again from then on: the
+  // unpack warps and the x producer look at the entry of the stage that used their slot last.  The
+  // ring length is a common multiple of both slot counts (nsb is 2, 3, 4 or 6).
+  uint64_t done[kDoneRing];
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
   int abort_flag;
@@ -299,8 +305,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStagesP; ++i) { mbar_init(smem_u32(&bars->full_p[i]), 1); mbar_init(smem_u32(&bars->empty_p[i]), kDequantSet); }
-    for (int i = 0; i < kStagesB; ++i) { mbar_init(smem_u32(&bars->full_b[i]), 1); mbar_init(smem_u32(&bars->empty_b[i]), 1); }
-    for (int i = 0; i < kStagesA; ++i) { mbar_init(smem_u32(&bars->full_a[i]), kDequantSet); mbar_init(smem_u32(&bars->empty_a[i]), 1); }
+    for (int i = 0; i < kStagesB; ++i) mbar_init(smem_u32(&bars->full_b[i]), 1);
+    for (int i = 0; i < kStagesA; ++i) mbar_init(smem_u32(&bars->full_a[i]), kDequantSet);
+    for (int i = 0; i < kDoneRing; ++i) mbar_init(smem_u32(&bars->done[i]), 1);
     mbar_init(smem_u32(&bars->acc_full), 1);
     mbar_init(smem_u32(&bars->acc_empty), kEpilogueWarps);
     bars->abort_flag = 0;
@@ -320,20 +327,24 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer: x tiles (B ring)
     if (lane == 0) {
-      uint32_t sb = 0, pb = 0;  // stage and phase, running across tiles
+      uint32_t sb = 0, it = 0;  // slot and stage counter, running across tiles
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const TileCoord tc_ = tile_coord(p, tile);
         bool ok = true;
         for (int ks = 0; ks < kstages; ++ks) {
           TC_T0();
-          if (!TC_WAIT1(smem_u32(&bars->empty_b[sb]), pb ^ 1, abort_flag)) { ok = false; break; }
+          if (it >= (uint32_t)kStagesB) {   // the stage that used this slot last has been multiplied
+            const uint32_t prev = it - (uint32_t)kStagesB;
+            if (!TC_WAIT1(smem_u32(&bars->done[prev % kDoneRing]), (prev / kDoneRing) & 1u, abort_flag)) { ok = false; break; }
+          }
           TC_ACC(pw1);
           const uint32_t bar = smem_u32(&bars->full_b[sb]);
           const uint32_t dst = smem_u32(ring_b + sb * b_stage_pitch);
           mbar_expect_tx(bar, b_stage_bytes);
           tma_load_2d(dst, &map_x, ks * kStageK, tc_.x_row0, bar);
           tma_load_2d(dst + b_sub_bytes, &map_x, ks * kStageK + kBlockK, tc_.x_row0, bar);
-          if (++sb == (uint32_t)kStagesB) { sb = 0; pb ^= 1; }
+          ++it;
+          if (++sb == (uint32_t)kStagesB) sb = 0;
         }
         if (!ok) break;
       }
@@ -365,7 +376,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = make_idesc(p.NT);
-      uint32_t tcount = 0, sa = 0, pa = 0, sb = 0, pb = 0;
+      uint32_t tcount = 0, sa = 0, pa = 0, sb = 0, pb = 0, itm = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
         TC_T0();
         if (!TC_WAIT1(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
@@ -390,10 +401,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           }
           TC_ACC(pw3);
           TC_T0();
-          // one arrival per ring and stage: the issuing thread pays for every commit, so a stage
-          // is 128 k (eight MMAs) deep
-          tcgen05_commit(smem_u32(&bars->empty_a[sa]));
-          tcgen05_commit(smem_u32(&bars->empty_b[sb]));
+          // one commit per stage (it costs the issuing thread about 65 cycles): a stage is 128 k
+          // (eight MMAs) deep and both rings are released through the same barrier
+          tcgen05_commit(smem_u32(&bars->done[itm % kDoneRing]));
+          ++itm;
           TC_ACC(pw4);
           if (++sa == (uint32_t)kStagesA) { sa = 0; pa ^= 1; }
           if (++sb == (uint32_t)kStagesB) { sb = 0; pb ^= 1; }
@@ -462,7 +473,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
       cur_chunk = -1;
       for (int ks = dset; ks < kstages; ks += 2) {
         const uint32_t it = tcount * (uint32_t)kstages + (uint32_t)ks;
-        const uint32_t sa = it % kStagesA, pa = (it / kStagesA) & 1u;
+        const uint32_t sa = it % kStagesA;
         const uint32_t sp = it % kStagesP, pp = (it / kStagesP) & 1u;
         // scale and bias of the two 32-k quarters of this thread's half (one group or two)
         uint32_t s_q[2], b_q[2];
@@ -518,7 +529,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           TC_ACC(pw3);
           if (q == 0) {
             TC_T0();
-            if (!TC_WAIT16(smem_u32(&bars->empty_a[sa]), pa ^ 1, abort_flag)) { ok = false; break; }
+            if (it >= (uint32_t)kStagesA) {   // the stage that used this A slot last has been multiplied
+              const uint32_t prev = it - (uint32_t)kStagesA;
+              if (!TC_WAIT16(smem_u32(&bars->done[prev % kDoneRing]), (prev / kDoneRing) & 1u, abort_flag)) { ok = false; break; }
+            }
             TC_ACC(pw2);
             tcgen05_fence_after();
             freed = true;
@@ -639,7 +653,7 @@ int pick_nt(int64_t M) {
 int x_stages(int nt, int bits) {
   const size_t fixed = 1024 + (size_t)stages_p(bits) * kTileN * 16 * bits + sizeof(Barriers) + 64;
   const size_t n = (kSmemMax - fixed) / ((size_t)nt * 256);
-  return (int)(n > (size_t)kMaxStagesB ? (size_t)kMaxStagesB : n);
+  return n >= 6 ? 6 : (n >= 4 ? 4 : (n >= 3 ? 3 : 2));   // a divisor of the length of the `done` ring
 }
 
 size_t smem_bytes(int nt, int bits) {
