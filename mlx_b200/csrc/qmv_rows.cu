@@ -780,15 +780,21 @@ bool pdl_enabled_rows() {
   return v == 1;
 }
 
-// Stages in flight per SM; B200Q_ROWS_INFLIGHT overrides (tuning).
-int rows_inflight() {
+// Stages the loader keeps in flight per SM.  More requests in flight dilute the first stage's arrival,
+// which is what the kernel waits for at its start; fewer starve a stream that is bound by HBM.
+// Measured (us per call, in flight = 1 / 2 / 3): M=16 14336x4096 4-bit 14.4 / 14.8 / 15.2 (two token
+// tiles make a stage MMA-bound); M=1 4096x14336 4-bit, three K phases, 15.2 / 15.8 / 15.7; M=1
+// 28672x8192 8-bit 48.1 / 45.9 / 45.6 (HBM-bound); M=16 28672x8192 8-bit 53.5 / 52.8 / 52.7.
+// B200Q_ROWS_INFLIGHT overrides (tuning).
+int rows_inflight(int mt, int bits, int nph) {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200Q_ROWS_INFLIGHT");
-    v = e ? atoi(e) : 3;
-    if ((v & 255) < 1) v = 1;
+    v = e ? atoi(e) : 0;
+    if (v < 0) v = 0;
   }
-  return v;
+  if (v > 0) return v;
+  return ((mt == 2 && bits <= 4) || nph > 1) ? 1 : 2;
 }
 
 template <int BITS, int G, int MT>
@@ -886,7 +892,7 @@ int qmv_rows(const QmmArgs& a, cudaStream_t st) {
   RowsPlan pl = make_plan(a);
   if (!pl.ok) return fail(B200Q_ERR_UNSUPPORTED, "[quantized_matmul] qmv_rows: unsupported problem");
   pl.prm.early = weights_constant() ? 1 : 0;
-  pl.prm.inflight = rows_inflight();
+  pl.prm.inflight = rows_inflight(pl.mt, a.bits, pl.prm.nph);
   if (a.ws && a.ws_bytes >= kStatusBytes)
     pl.prm.status = reinterpret_cast<uint32_t*>(static_cast<char*>(a.ws) + a.ws_bytes - kStatusBytes);
   int rc = B200Q_ERR_UNSUPPORTED;
