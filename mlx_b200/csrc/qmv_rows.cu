@@ -782,10 +782,11 @@ bool pdl_enabled_rows() {
 
 // Stages the loader keeps in flight per SM.  More requests in flight dilute the first stage's arrival,
 // which is what the kernel waits for at its start; fewer starve a stream that is bound by HBM.
-// Measured (us per call, in flight = 1 / 2 / 3): M=16 14336x4096 4-bit 14.4 / 14.8 / 15.2 (two token
-// tiles make a stage MMA-bound); M=1 4096x14336 4-bit, three K phases, 15.2 / 15.8 / 15.7; M=1
-// 28672x8192 8-bit 48.1 / 45.9 / 45.6 (HBM-bound); M=16 28672x8192 8-bit 53.5 / 52.8 / 52.7.
-// B200Q_ROWS_INFLIGHT overrides (tuning).
+// Measured (us per call, in flight = 1 / 2 / 3): M=16 14336x4096 4-bit 14.4 / 14.8 / 15.2; M=1
+// 4096x14336 4-bit 15.2 / 15.8 / 15.7; M=1 8192x28672 4-bit 35.8 / 36.9 / 36.9; M=1 28672x8192 4-bit
+// 28.5 / 28.5 / 28.5; M=1 28672x8192 8-bit 48.1 / 45.9 / 45.6; M=16 28672x8192 8-bit 53.5 / 52.8 / 52.7:
+// one for 2- and 4-bit weights, two for 8-bit (twice the bytes per stage, the stream closest to the
+// HBM bound).  B200Q_ROWS_INFLIGHT overrides (tuning).
 int rows_inflight(int mt, int bits, int nph) {
   static int v = -1;
   if (v < 0) {
@@ -794,7 +795,8 @@ int rows_inflight(int mt, int bits, int nph) {
     if (v < 0) v = 0;
   }
   if (v > 0) return v;
-  return ((mt == 2 && bits <= 4) || nph > 1) ? 1 : 2;
+  (void)mt; (void)nph;
+  return bits >= 8 ? 2 : 1;
 }
 
 template <int BITS, int G, int MT>
