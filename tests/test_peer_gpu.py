@@ -20,6 +20,20 @@ def test_sharded_matmul_allgather_two_ranks():
     assert res.returncode == 0 and res.stdout.count("PEER-OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs on one machine")
+def test_sharded_matmul_through_the_copy_kernel_two_ranks():
+    """The same worker with B200Q_PUSH=1: prefill-size products store their block locally and
+    peer_push_kernel moves it to the other rank and signals (the form chosen by default above four
+    ranks); every gathered result is checked against the oracle as before."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", B200Q_PUSH="1")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29543",
+                          os.path.join(root, "tests", "peer_worker.py")], cwd=root, env=env, capture_output=True,
+                         text=True, timeout=600)
+    assert res.returncode == 0 and res.stdout.count("PEER-OK") == 2, res.stdout[-3000:] + res.stderr[-3000:]
+
+
 def test_bounded_wait_runs_out_and_is_reported():
     """A rank that never signals: the bounded wait of the exchange gives up after its limit (set to
     50 ms here), stores code 6 in the status word and lets the stream go on; the host-side check
