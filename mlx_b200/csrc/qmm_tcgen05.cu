@@ -377,6 +377,10 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
     if (lane == 0) {
       const uint32_t idesc = make_idesc(p.NT);
       uint32_t tcount = 0, sa = 0, pa = 0, sb = 0, pb = 0, itm = 0;
+      // The commit of a stage is issued after the FIRST MMA of the next one: its 65 cycles then pass
+      // while the tensor pipe works, not between two stages.  (The barrier then also covers that one
+      // MMA: the stage is released 128 cycles later.)
+      bool commit_due = false;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
         TC_T0();
         if (!TC_WAIT1(smem_u32(&bars->acc_empty), (tcount & 1) ^ 1, abort_flag)) break;
@@ -398,18 +402,24 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             tcgen05_mma_ts(tmem_acc, tmem_a + sa * 64 + kk * 8,
                            make_sw128_desc(b_addr + (kk >> 2) * b_sub_bytes + (kk & 3) * 32), idesc,
                            (ks | kk) != 0 ? 1u : 0u);
+            if (kk == 0 && commit_due) {
+              // one commit per stage: a stage is 128 k (eight MMAs) deep and both rings are released
+              // through the same barrier
+              tcgen05_commit(smem_u32(&bars->done[(itm - 1) % kDoneRing]));
+              commit_due = false;
+            }
           }
           TC_ACC(pw3);
-          TC_T0();
-          // one commit per stage (it costs the issuing thread about 65 cycles): a stage is 128 k
-          // (eight MMAs) deep and both rings are released through the same barrier
-          tcgen05_commit(smem_u32(&bars->done[itm % kDoneRing]));
+          commit_due = true;
           ++itm;
-          TC_ACC(pw4);
           if (++sa == (uint32_t)kStagesA) { sa = 0; pa ^= 1; }
           if (++sb == (uint32_t)kStagesB) { sb = 0; pb ^= 1; }
         }
         if (!ok) break;
+        if (commit_due) {
+          tcgen05_commit(smem_u32(&bars->done[(itm - 1) % kDoneRing]));
+          commit_due = false;
+        }
         tcgen05_commit(smem_u32(&bars->acc_full));
       }
       TC_OUT(4, pw0); TC_OUT(5, pw1); TC_OUT(6, pw2); TC_OUT(7, clock64() - prof_entry); TC_OUT(14, pw3); TC_OUT(15, pw4);
