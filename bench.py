@@ -389,6 +389,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def align_ranks():
+        """N > 1: a one-element all_reduce on the timing stream right before a timed interval.  The host
+        barrier lets the ranks go hundreds of microseconds apart, and a rank that starts late keeps the
+        others waiting for its flags inside their interval; after the collective all streams continue
+        within a few microseconds of each other."""
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(torch.zeros(1, device=dev))
+
     def max_over_ranks(v: float) -> float:
         if world == 1:
             return v
@@ -496,6 +505,7 @@ def main():
         sampler.start()
         time.sleep(0.3)
         barrier()
+        align_ranks()
         queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             e0.record(stream)
@@ -506,6 +516,7 @@ def main():
         sampler.start()
         time.sleep(0.3)
         barrier()
+        align_ranks()
         queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             e0.record(stream)
@@ -532,6 +543,7 @@ def main():
         g2.replay()
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        align_ranks()
         queue_delay(torch, stream)
         with torch.cuda.stream(stream):
             f0.record(stream)
