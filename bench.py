@@ -375,7 +375,7 @@ def main():
     lib = _lib.load()
     # The weights of this benchmark are constants (as in inference): the decode kernel may request
     # them while the previous kernel of the stream is still finishing.
-    lib.b200q_set_weights_constant(1)
+    mb.set_weights_constant(True)
     P = lambda t: ctypes.c_void_p(t.data_ptr())
     hbm_peak, tf_peak, peak_src = measured_peaks()
 

@@ -6,7 +6,7 @@ Drop-in for the reference's ``quantize`` / ``dequantize`` / ``quantized_matmul``
 """
 __all__ = ["quantize", "dequantize", "quantized_matmul", "gather_qmm", "gather_qmm_chain", "gather_qmm_swiglu",
            "quantized_embedding",
-           "qmm_kernel_name"]
+           "qmm_kernel_name", "set_weights_constant"]
 
 
 def __getattr__(name):

@@ -10,6 +10,7 @@ Invalid arguments raise ``ValueError`` (the reference's std::invalid_argument).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -299,6 +300,19 @@ def quantized_embedding(ids: torch.Tensor, w: torch.Tensor, scales: torch.Tensor
 
 
 # ------------------------------------------------------------------- quantized_matmul
+_weights_constant = os.environ.get("B200Q_WEIGHTS_CONSTANT", "") == "1"
+
+
+def set_weights_constant(on: bool) -> None:
+    """The caller's promise that packed weights, scales and biases are not written by whatever
+    precedes a matmul on its stream (b200q_set_weights_constant): the decode kernel may then request
+    them before the previous kernel has finished.  quantized_matmul suspends the promise for a call
+    in which it had to cast or copy one of the three itself (that copy IS the preceding kernel)."""
+    global _weights_constant
+    _weights_constant = bool(on)
+    _lib.load().b200q_set_weights_constant(int(_weights_constant))
+
+
 def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
                      biases: Optional[torch.Tensor] = None, transpose: bool = True,
                      group_size: Optional[int] = None, bits: Optional[int] = None,
@@ -311,6 +325,7 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
     if not dtype.is_floating_point or dtype not in _DT:
         raise ValueError(f"[quantized_matmul] Only real floating types are supported but x.dtype() == {x.dtype}.")
     dev = _require_cuda("quantized_matmul", x, w, scales, biases)
+    given = (w, scales, biases)
     x, scales, biases = x.to(dtype), scales.to(dtype), biases.to(dtype)
 
     vector = x.ndim == 1
@@ -346,8 +361,17 @@ def quantized_matmul(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
         y = torch.empty(out_lead + (M, N), dtype=dtype, device=dev)
         need = lib.b200q_qmm_workspace_bytes(_DT[dtype], batch, M, N, K, group_size, bits, int(transpose))
         ws = _workspaces.get(dev, need, "qmm")
-        rc = lib.b200q_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(y), _DT[dtype], batch, M, N, K,
-                           group_size, bits, int(transpose), w_stride, _ptr(ws), ws.numel(), _stream(x))
+        # a weight operand this function has just cast or copied was written by the kernel right
+        # before the matmul on this stream: no early weight loads for this call
+        fresh = _weights_constant and any(a.data_ptr() != b.data_ptr() for a, b in zip((w, scales, biases), given))
+        if fresh:
+            lib.b200q_set_weights_constant(0)
+        try:
+            rc = lib.b200q_qmm(_ptr(x), _ptr(w), _ptr(scales), _ptr(biases), _ptr(y), _DT[dtype], batch, M, N, K,
+                               group_size, bits, int(transpose), w_stride, _ptr(ws), ws.numel(), _stream(x))
+        finally:
+            if fresh:
+                lib.b200q_set_weights_constant(1)
     _lib.check(rc)
     if _checked():
         read_workspace_status(ws, torch.cuda.current_stream(dev).cuda_stream, "qmm")

@@ -128,3 +128,15 @@ def test_embedding_and_gated_mlp_reject_on_host():
     assert glu(ws=256) == _lib.ERR_WORKSPACE
     assert lib.b200q_gather_qmm_swiglu_workspace_bytes(8, 4, 1, 256, 256) > lib.b200q_gather_qmm_workspace_bytes(
         _lib.BF16, 8, 8, 4, 1, 256, 256, 64, 4, 1)
+
+
+def test_weights_constant_promise_toggles_on_the_host():
+    """b200q_set_weights_constant is host state only; the Python wrapper mirrors it so that
+    quantized_matmul can suspend the promise around a call whose weights it has just copied."""
+    import mlx_b200 as mb
+    from mlx_b200 import ops
+
+    mb.set_weights_constant(True)
+    assert ops._weights_constant is True
+    mb.set_weights_constant(False)
+    assert ops._weights_constant is False
